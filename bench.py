@@ -1,0 +1,378 @@
+"""Benchmark of the decode-attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decode-layer pass over one batch: QK-Norm + RoPE + KV append for the new
+token, attention over the whole KV cache and, on N > 1 GPUs, the all-gather of the output.
+The headline workload is the Qwen3-32B-shaped long-context case: 64 query / 8 KV heads,
+head_dim 128, batch 4, 131072 cached positions per sequence, BF16, the cache paged in
+256-token pool blocks; KV heads are split over the N GPUs (strong scaling). All inputs are
+seeded synthetic N(0, 1) tensors.
+
+Rank 0 prints one JSON line: `value` is microseconds per layer with everything resident in
+HBM (CUDA-graph replay of K steps, CUDA events, max over ranks); `e2e` is the same through
+gqa_session_step with host buffers (H2D of the new token's rows, kernels, D2H of the output,
+every step); `roofline` is for the streaming attention kernels alone; `cpu_baseline` times the
+CPU oracle on a bounded sample of the same workload.
+
+--impl reference times the reference's CPU attention path, restated in oracle/gqa_oracle.c
+(the reference's own CPU sources need Armadillo and glog, which are not installed, and its
+score computation is commented out), with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HEAD_DIM = 128
+BLOCK_TOKENS = 256
+WORKLOADS = {
+    # name: query heads, kv heads, batch, cached length
+    "qwen3-32b-bf16-b4-ctx131072": (64, 8, 4, 131072),
+    "qwen3-4b-bf16-b1-ctx32768": (32, 8, 1, 32768),
+    "qwen3-4b-bf16-b1-ctx1024": (32, 8, 1, 1024),
+}
+DEFAULT_WORKLOAD = "qwen3-32b-bf16-b4-ctx131072"
+MIN_RESIDENT_BYTES = 1 << 30  # distinct KV bytes cycled per GPU, several times the 126 MB L2
+
+
+def algorithmic_bytes(hq: int, hkv: int, lens) -> int:
+    """K and V read once per KV head, q read, out written (BF16)."""
+    return sum(2 * l * hkv * HEAD_DIM * 2 for l in lens) + 2 * len(lens) * hq * HEAD_DIM * 2
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.rows.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        clocks, reasons, mx = [], set(), None
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for row in self.rows:
+            try:
+                clocks.append(float(row[0]))
+                mx = float(row[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, row[2:]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        med = clocks[len(clocks) // 2] if clocks else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's CPU attention on a bounded sample
+# ---------------------------------------------------------------------------------------------
+def cpu_sample_us_per_layer(hq: int, hkv: int, batch: int, length: int, reps: int,
+                            warmup: int) -> dict:
+    """Times one sequence (all heads) on all host threads and scales by the batch size."""
+    import numpy as np
+    from oracle import oracle
+
+    sys.path.insert(0, str(ROOT / "tests" / "golden"))
+    import cases
+
+    rng = np.random.default_rng(5)
+    sample_len = length
+    kv_dim = hkv * HEAD_DIM
+
+    def normal_bf16(n: int) -> "np.ndarray":
+        out = np.empty(n, dtype=np.uint16)
+        piece = 1 << 24
+        for start in range(0, n, piece):
+            m = min(piece, n - start)
+            out[start:start + m] = cases.to_bf16_bits(rng.standard_normal(m, dtype=np.float32))
+        return out
+
+    k = normal_bf16(sample_len * kv_dim)
+    v = normal_bf16(sample_len * kv_dim)
+    q = normal_bf16(hq * HEAD_DIM).reshape(1, hq, HEAD_DIM)
+    threads = oracle.max_threads()
+    times = []
+    for i in range(warmup + reps):
+        t0 = time.perf_counter()
+        oracle.gqa_decode(q, k, v, [sample_len], hkv=hkv, stride_block=sample_len * kv_dim,
+                          stride_token=kv_dim, stride_head=HEAD_DIM, block_tokens=sample_len,
+                          accum=0, threads=0)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    per_seq = sum(times) / len(times)
+    return {"value": per_seq * batch * 1e6, "unit": "us/layer", "cores": threads, "kind": "port",
+            "sample": f"1 of {batch} sequences ({hq} q heads, {hkv} kv heads, {sample_len} keys, "
+                      f"FP32 math on BF16 values), all {threads} host threads, scaled x{batch}",
+            "seconds_per_sample": per_seq}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    hq, hkv, batch, length = WORKLOADS[args.workload]
+    steps = max(1, min(args.steps, 5))
+    res = cpu_sample_us_per_layer(hq, hkv, batch, length, reps=steps, warmup=min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": "gqa_decode_attn_us_per_layer", "value": res["value"],
+        "unit": "us/layer", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
+        "ms_per_step": res["value"] / 1e3, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "num_q_heads": hq, "num_kv_heads": hkv,
+                   "batch": batch, "kv_len": length, "note": "CPU oracle port of the reference's "
+                   "FP32 CPU attention; each step is the bounded sample described in cpu_baseline"},
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": "us/layer", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import llminfer_b200 as gqa
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    comm = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        ident = [gqa.ShardComm.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ident, src=0)
+        comm = gqa.ShardComm(ident[0], world, rank)
+
+    hq_total, hkv_total, batch, length = WORKLOADS[args.workload]
+    shard = gqa.shard_plan(hq_total, hkv_total, world, rank)
+    hq, hkv = shard["num_local_q_heads"], shard["num_local_kv_heads"]
+    pos = length - 1
+    lens = [length] * batch
+    blocks_per_seq = length // BLOCK_TOKENS
+    blocks_per_slot = batch * blocks_per_seq
+    slot_bytes = 2 * blocks_per_slot * hkv * BLOCK_TOKENS * HEAD_DIM * 2
+    slots = max(1, -(-MIN_RESIDENT_BYTES // slot_bytes))
+    num_blocks = slots * blocks_per_slot
+    layout = gqa.layout_pool(num_blocks, BLOCK_TOKENS, hkv)
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(20260614 + rank)
+    pool_elems = num_blocks * hkv * BLOCK_TOKENS * HEAD_DIM
+    k_pool = torch.empty(pool_elems, dtype=torch.bfloat16, device=dev)
+    v_pool = torch.empty(pool_elems, dtype=torch.bfloat16, device=dev)
+    piece = 1 << 26
+    for pool in (k_pool, v_pool):
+        for start in range(0, pool_elems, piece):
+            n = min(piece, pool_elems - start)
+            pool[start:start + n] = torch.randn(n, device=dev, generator=gen).to(torch.bfloat16)
+    cpu_gen = torch.Generator().manual_seed(7)
+    tables = []
+    for s in range(slots):
+        perm = torch.randperm(blocks_per_slot, generator=cpu_gen) + s * blocks_per_slot
+        tables.append(perm.to(torch.int32).view(batch, blocks_per_seq).to(dev))
+    q_raw = torch.randn(batch, hq, HEAD_DIM, device=dev, generator=gen).to(torch.bfloat16)
+    k_new = torch.randn(batch, hkv, HEAD_DIM, device=dev, generator=gen).to(torch.bfloat16)
+    v_new = torch.randn(batch, hkv, HEAD_DIM, device=dev, generator=gen).to(torch.bfloat16)
+    weight = (1.0 + 0.05 * torch.randn(2 * HEAD_DIM, device=dev, generator=gen)).to(torch.bfloat16)
+    q_rot = torch.empty_like(q_raw)
+    out = torch.empty(batch, hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+    gathered = torch.empty(world, batch, hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+    positions_dev = torch.full((batch,), pos, dtype=torch.int32, device=dev)
+    lens_dev = torch.tensor(lens, dtype=torch.int32, device=dev)
+    workspace = gqa.binding.workspace_for(batch, hq, hkv, dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    plan = gqa.decode_plan(dtype=2, batch=batch, num_q_heads=hq, num_kv_heads=hkv, layout=layout,
+                           seq_lens=lens, paged=True, blocks_per_seq=blocks_per_seq,
+                           device_lens=True, sm_count=torch.cuda.get_device_properties(dev).multi_processor_count,
+                           workspace_bytes=workspace.numel() * 4)
+
+    def attention(slot: int) -> None:
+        kw = dict(num_kv_heads=hkv, layout=layout, seq_lens=lens, seq_lens_dev=lens_dev,
+                  block_table=tables[slot], workspace=workspace, status=status)
+        if comm is None:
+            gqa.decode(q_rot, k_pool, v_pool, out, **kw)
+        else:
+            gqa.decode_sharded(comm, gathered, q_rot, k_pool, v_pool, out, **kw)
+
+    def step(slot: int) -> None:
+        gqa.qk_norm_rope_append(q_raw, k_new, v_new, weight, k_pool, v_pool, layout=layout,
+                                positions=[pos] * batch, positions_dev=positions_dev,
+                                q_out=q_rot, block_table=tables[slot])
+        attention(slot)
+
+    def barrier() -> None:
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed_graph(fn, steps: int, warmup: int) -> float:
+        """Warm-up eagerly, capture `steps` calls in one CUDA graph, time one replay."""
+        for i in range(warmup):
+            fn(i % slots)
+        barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(steps):
+                fn(i % slots)
+        graph.replay()  # untimed: first replay uploads the graph
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        stop.record()
+        barrier()
+        return max_over_ranks(start.elapsed_time(stop))
+
+    steps, warmup = args.steps, max(args.warmup, 3)
+    with ClockSampler(local_rank) as clocks:
+        total_ms = timed_graph(step, steps, warmup)
+        attn_ms = timed_graph(attention, steps, warmup)
+    clock_info = clocks.summary()
+    us_per_layer = total_ms * 1e3 / steps
+    attn_us = attn_ms * 1e3 / steps
+    assert int(status.item()) == 0, "a bounded device wait ran out"
+
+    # ---- end to end through the host-buffer entry point -----------------------------------
+    session = gqa.Session(batch, hq, hkv, length)
+    pin = lambda t: t.cpu().pin_memory()
+    q_host, k_host, v_host = pin(q_raw), pin(k_new), pin(v_new)
+    out_host = torch.empty(world if comm else 1, batch, hq, HEAD_DIM, dtype=torch.bfloat16).pin_memory()
+    def e2e_step(i: int) -> None:
+        session.step(q_host, k_host, v_host, weight, k_pool, v_pool, layout, [pos] * batch,
+                     out_host, block_table=tables[i % slots], comm=comm)
+    for i in range(warmup):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        e2e_step(i)
+    barrier()
+    e2e_us = max_over_ranks((time.perf_counter() - t0) * 1e3) * 1e3 / steps
+    session.close()
+    h2d = (hq + 2 * hkv) * HEAD_DIM * 2 * batch + 8 * batch
+    d2h = out_host.numel() * 2
+
+    peak, peak_kind = measured_peak_gbs()
+    rank_bytes = algorithmic_bytes(hq, hkv, lens)
+    achieved = rank_bytes / (attn_us * 1e-6) / 1e9
+    line = {
+        "metric": "gqa_decode_attn_us_per_layer", "value": us_per_layer, "unit": "us/layer",
+        "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": us_per_layer / 1e3,
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "num_q_heads": hq_total, "num_kv_heads": hkv_total,
+                   "head_dim": HEAD_DIM, "batch": batch, "kv_len": length,
+                   "kv_layout": f"paged pool, {BLOCK_TOKENS}-token blocks, shuffled block order",
+                   "parallelism": f"kv-head-parallel x{world}",
+                   "l2": f"inputs larger than L2: {slots} cache slot(s) of "
+                         f"{slot_bytes / 2**20:.0f} MiB cycled per GPU",
+                   "step": "qk-norm+rope+append, split attention, lse combine"
+                           + (", nccl all-gather" if world > 1 else ""),
+                   "split_chunks": plan["split_chunks"], "ctas": plan["num_ctas"],
+                   "items": plan["num_items"]},
+        "hbm_tbs_aggregate": achieved * world / 1e3,
+        "attention_only_us_per_layer": attn_us,
+        "roofline": {"bound": "hbm", "kernel": "gqa_decode_stream_bf16 (+ lse combine)",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": peak_kind, "frac_of_8tbs_nominal": achieved / 8000.0,
+                     "algorithmic_bytes_per_launch": rank_bytes, "traffic": None},
+        "e2e": {"value": e2e_us, "unit": "us/layer", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": 3 * steps,
+        "clocks": clock_info,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        hq0, hkv0, b0, l0 = WORKLOADS[args.workload]
+        cpu = cpu_sample_us_per_layer(hq0, hkv0, b0, l0, reps=2, warmup=1)
+        line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if rank == 0:
+        print(json.dumps(line))
+    if comm is not None:
+        comm.close()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=tuple(WORKLOADS), default=DEFAULT_WORKLOAD)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

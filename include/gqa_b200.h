@@ -1,0 +1,314 @@
+/*
+ * gqa_b200 — C ABI of the B200 (sm_100a) decode-phase grouped-query attention library.
+ *
+ * One hot path of the LLMInfer engine is provided here and nothing else: Qwen3 decode
+ * attention (one query token per sequence against a BF16 or FP32 KV cache), with the
+ * QK-Norm + RoPE + KV-append stage in front of it, the KV block pool it reads from and the
+ * KV-head-parallel partition across the GPUs of one node. Every entry point takes plain
+ * pointers and sizes, returns a status code, never aborts, never synchronises the device
+ * (except where stated) and has NO CPU fallback: without a CUDA device the compute entry
+ * points return GQA_ERR_CUDA.
+ *
+ * Each declaration names the interface of the reference engine it stands in for, as
+ * file:line inside the reference project.
+ */
+#ifndef GQA_B200_H
+#define GQA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GQA_B200_ABI_VERSION 1
+
+/* ---- status codes ------------------------------------------------------------------- */
+#define GQA_OK 0
+#define GQA_ERR_NULL (-1)        /* a required pointer is null */
+#define GQA_ERR_DTYPE (-2)       /* dtype is not GQA_DTYPE_F32 / GQA_DTYPE_BF16 */
+#define GQA_ERR_SHAPE (-3)       /* head counts, head_dim, batch or layout are unsupported */
+#define GQA_ERR_ALIGN (-4)       /* a pointer or stride breaks the 16-byte rule */
+#define GQA_ERR_RANGE (-5)       /* a position or length is outside the cache */
+#define GQA_ERR_WORKSPACE (-6)   /* the workspace is too small for any valid split */
+#define GQA_ERR_CUDA (-7)        /* a CUDA call failed (or no device / driver) */
+#define GQA_ERR_UNSUPPORTED (-8) /* valid request this build does not cover */
+#define GQA_ERR_COMM (-9)        /* NCCL is missing or a collective failed */
+#define GQA_ERR_POOL (-10)       /* KV pool: out of blocks, bad sequence or handle */
+#define GQA_ERR_TIMEOUT (-11)    /* a bounded device wait ran out (see status word) */
+
+/* dtype values are the reference's base::DataType values (code/include/base/base.h:51-58). */
+#define GQA_DTYPE_F32 1
+#define GQA_DTYPE_BF16 2
+
+/* Keys per chunk: the unit in which key ranges are cut, staged and split. */
+#define GQA_CHUNK_KEYS 32
+
+const char* gqa_status_string(int status);
+int gqa_abi_version(void);
+
+/* ---- KV cache addressing ------------------------------------------------------------- */
+/*
+ * Element (block, token, kv_head, channel) of a cache lives at
+ *     block * stride_block + token * stride_token + kv_head * stride_head + channel
+ * (in elements). Two layouts are used:
+ *   - the reference's contiguous cache [layer, max_seq_len, kv_dim]
+ *     (code/source/model/qwen3_fused.cpp:488-489): block = layer, block_tokens =
+ *     max_seq_len, stride_block = max_seq_len * kv_dim, stride_token = kv_dim,
+ *     stride_head = head_dim; gqa_layout_reference() fills it in;
+ *   - the paged pool [block, kv_head, block_tokens, head_dim], each head's share of a
+ *     block contiguous (64 KiB for 256 BF16 tokens); gqa_layout_pool() fills it in.
+ * K and V caches share one layout and differ in base pointer only.
+ */
+typedef struct gqa_kv_layout {
+    int32_t block_tokens;
+    int32_t num_blocks;
+    int64_t stride_block;
+    int64_t stride_token;
+    int64_t stride_head;
+} gqa_kv_layout;
+
+int gqa_layout_reference(int32_t layer_num, int32_t max_seq_len, int32_t num_kv_heads,
+                         int32_t head_dim, gqa_kv_layout* out);
+int gqa_layout_pool(int32_t num_blocks, int32_t block_tokens, int32_t num_kv_heads,
+                    int32_t head_dim, gqa_kv_layout* out);
+
+/* ---- decode attention ---------------------------------------------------------------- */
+/*
+ * Stands in for kernel::mha_kernel_cu (code/source/op/kernel/cuda/mha_kernel.cu:440-529,
+ * declared code/source/op/kernel/cuda/mha_kernel.cuh:7-21) and its three kernels
+ * (:44-208 single pass, :210-388 KV split, :399-438 combine), generalised to a batch of
+ * sequences and to a paged cache.
+ *
+ *   q, out          [batch, num_q_heads, head_dim], dtype elements, 16-byte aligned.
+ *   k_cache/v_cache bases of the caches, `layout` addressing, dtype elements.
+ *   seq_lens_host   [batch] cached positions attended (pos + 1) per sequence, or null.
+ *   seq_lens_dev    the same on the device, or null. With a device array the kernels read
+ *                   lengths from it (a captured graph stays valid as lengths grow) and the
+ *                   host copy, when also given, is used for split planning only. Without
+ *                   it the host lengths must all be equal (they are passed by value).
+ *   plan_len_hint   planning length when only seq_lens_dev is given (0: block capacity).
+ *   block_table_dev [batch, blocks_per_seq] physical block of each logical block, or
+ *                   null: every sequence then reads block `fixed_block` (the reference's
+ *                   layer_id) and batch must be 1.
+ *   workspace       FP32 scratch for split partials, gqa_decode_plan() gives the size; may
+ *                   be null when the plan needs no split. Contents need no initialisation.
+ *   split_keys      0 = choose from lengths and SM count; otherwise keys per split
+ *                   (rounded up to a multiple of GQA_CHUNK_KEYS). The value of a head's
+ *                   output depends on (length, split_keys) only, never on batch size, head
+ *                   count or rank count, so equal split_keys give bit-equal results.
+ *   max_ctas        0 = one CTA per SM; otherwise an upper bound on the grid.
+ *   status_dev      optional device int32, set non-zero by a kernel whose bounded wait ran
+ *                   out (it then skips its work instead of hanging).
+ *   stream          cudaStream_t (null = default stream), as the reference passes it.
+ */
+typedef struct gqa_decode_params {
+    int32_t dtype;
+    int32_t batch;
+    int32_t num_q_heads;
+    int32_t num_kv_heads;
+    int32_t head_dim;
+    int32_t blocks_per_seq;
+    int32_t fixed_block;
+    int32_t split_keys;
+    int32_t max_ctas;
+    int32_t plan_len_hint;
+    gqa_kv_layout layout;
+    const void* q;
+    const void* k_cache;
+    const void* v_cache;
+    void* out;
+    void* workspace;
+    size_t workspace_bytes;
+    const int32_t* seq_lens_host;
+    const int32_t* seq_lens_dev;
+    const int32_t* block_table_dev;
+    int32_t* status_dev;
+    void* stream;
+} gqa_decode_params;
+
+typedef struct gqa_decode_plan_info {
+    int32_t split_chunks;     /* chunks of GQA_CHUNK_KEYS keys per split */
+    int32_t max_splits;       /* splits of the longest sequence */
+    int32_t num_items;        /* (sequence, kv head, split) work items (upper bound) */
+    int32_t num_ctas;         /* grid of the streaming kernel */
+    int32_t needs_combine;    /* 1 when a second, LSE-combine launch follows */
+    int32_t reserved;
+    size_t workspace_bytes;   /* scratch the chosen plan needs */
+} gqa_decode_plan_info;
+
+/*
+ * Host only: validates `p` (without touching its device pointers) and chooses the split.
+ * sm_count 0 asks the current device. Replaces the reference's fixed rule "split every 32
+ * keys once seq_len > 128" (mha_kernel.cu:505-517) and its workspace sizing
+ * (code/source/model/qwen3_fused.cpp:502). When p->workspace_bytes is non-zero the plan is
+ * kept within it; pass 0 to ask how much the unconstrained plan wants.
+ */
+int gqa_decode_plan(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out);
+
+/* Launches the attention kernels on p->stream. Asynchronous. */
+int gqa_decode(const gqa_decode_params* p);
+
+/* ---- front stage: QK-Norm + RoPE + KV append ------------------------------------------ */
+/*
+ * Stands in for kernel::fused_qk_norm_rope_kernel_cu
+ * (code/source/op/kernel/cuda/rmsnorm_kernel.cu:205-290) and for the KV-row placement done
+ * by Model::slice_kv_cache (code/source/model/model.cpp:90-107) together with the
+ * destination select of the QKV GEMV (code/source/op/kernel/cuda/matmul_kernel.cu:238-246).
+ *
+ * Per sequence b at position pos_b: q[b] is RMS-normalised per head (eps), scaled by
+ * qk_weight[0:head_dim], rotated (rotate-half pairs (i, i + head_dim/2)) and written to
+ * q_out[b]; k_new[b] likewise with qk_weight[head_dim:2*head_dim], written to the K cache
+ * row of pos_b; v_new[b] is copied unchanged to the V cache row. BF16 only, FP32 math,
+ * one rounding at the end.
+ *   q, q_out        [batch, num_q_heads, head_dim]; may alias (the reference works in place).
+ *   k_new, v_new    [batch, num_kv_heads, head_dim]. k_new may already be the cache row
+ *                   (reference behaviour: the GEMV wrote it there); v_new null = V untouched.
+ *   sin_cache/cos_cache  FP32 [table_len, head_dim/2] as built by gqa_sin_cos_cache, or
+ *                   both null: angles are then computed in the kernel with the same formula.
+ *   positions_host  [batch] or null; positions_dev [batch] on the device or null. One of
+ *                   them is required; the device array wins.
+ */
+typedef struct gqa_front_params {
+    int32_t batch;
+    int32_t num_q_heads;
+    int32_t num_kv_heads;
+    int32_t head_dim;
+    int32_t blocks_per_seq;
+    int32_t fixed_block;
+    int32_t table_len;
+    float eps;
+    gqa_kv_layout layout;
+    const void* q;
+    void* q_out;
+    const void* k_new;
+    const void* v_new;
+    const void* qk_weight;
+    void* k_cache;
+    void* v_cache;
+    const float* sin_cache;
+    const float* cos_cache;
+    const int32_t* positions_host;
+    const int32_t* positions_dev;
+    const int32_t* block_table_dev;
+    void* stream;
+} gqa_front_params;
+
+int gqa_qk_norm_rope_append(const gqa_front_params* p);
+
+/*
+ * Stands in for kernel::sin_cos_cache_precompute_cu
+ * (code/source/op/kernel/cuda/rope_kernel.cu:6-46): FP32 tables [max_seq_len, head_dim/2],
+ * freq_i = 1 / powf(1e6, 2i / head_dim), sincosf((float)pos * freq_i).
+ */
+int gqa_sin_cos_cache(float* sin_cache, float* cos_cache, int32_t head_dim, int32_t max_seq_len,
+                      void* stream);
+
+/* ---- one decode step from host buffers ------------------------------------------------ */
+/*
+ * What a caller that keeps only the KV cache on the device does per layer and token: copy
+ * the new token's q/k/v rows (host, ideally pinned) to the device, run the front stage and
+ * the attention, copy the attention output back and wait for it. The session owns the
+ * device staging buffers, the split workspace and a stream, all allocated at creation.
+ * Mirrors one iteration of the reference's layer loop around attention
+ * (code/source/model/qwen3_fused.cpp:517-553) minus its GEMVs.
+ */
+typedef struct gqa_session gqa_session;
+
+int gqa_session_create(int32_t dtype, int32_t max_batch, int32_t num_q_heads,
+                       int32_t num_kv_heads, int32_t head_dim, int32_t max_seq_len,
+                       gqa_session** out);
+void gqa_session_destroy(gqa_session* s);
+
+/*
+ * q_host/k_host/v_host/out_host: [batch, heads, head_dim] BF16 on the host. positions_host
+ * [batch]: the new token's position per sequence; it attends positions 0..pos. Blocks until
+ * out_host is filled. Cache pointers, layout and block table as in gqa_decode_params.
+ */
+int gqa_session_step(gqa_session* s, int32_t batch, const void* q_host, const void* k_host,
+                     const void* v_host, const void* qk_weight_dev, void* k_cache, void* v_cache,
+                     const gqa_kv_layout* layout, const int32_t* positions_host,
+                     const int32_t* block_table_dev, int32_t blocks_per_seq,
+                     int32_t fixed_block, void* out_host);
+
+/*
+ * The same step on one rank of a KV-head-parallel group (see gqa_comm below): the session was
+ * created with the LOCAL head counts, host rows are this rank's heads, and after the local
+ * attention the outputs of all ranks are gathered on the device (ncclAllGather) before the
+ * copy back. gathered_host is [nranks, batch, local_q_heads, head_dim]. Collective: every
+ * rank of `comm` must call it.
+ */
+struct gqa_comm;
+int gqa_session_step_sharded(gqa_session* s, struct gqa_comm* comm, int32_t batch,
+                             const void* q_host, const void* k_host, const void* v_host,
+                             const void* qk_weight_dev, void* k_cache, void* v_cache,
+                             const gqa_kv_layout* layout, const int32_t* positions_host,
+                             const int32_t* block_table_dev, int32_t blocks_per_seq,
+                             int32_t fixed_block, void* gathered_host);
+
+/* ---- KV block pool -------------------------------------------------------------------- */
+/*
+ * Host-side owner of a paged KV cache: block geometry with every head's share of a block
+ * 1024-byte aligned (the staging tiles are swizzled in 1 KiB atoms and bulk tensor copies
+ * want 16-byte strides), a free list, and one block table row per sequence. Takes the
+ * place of the contiguous per-layer caches the reference allocates from its
+ * CUDADeviceAllocator pool (code/source/model/qwen3_fused.cpp:483-489,
+ * code/source/base/alloc_cu.cpp:7-79). The pool does not allocate device memory: the
+ * caller provides K and V arenas of gqa_kv_pool_bytes() each.
+ */
+typedef struct gqa_kv_pool gqa_kv_pool;
+
+size_t gqa_kv_pool_bytes(int32_t num_blocks, int32_t block_tokens, int32_t num_kv_heads,
+                         int32_t head_dim, int32_t dtype);
+int gqa_kv_pool_create(int32_t num_blocks, int32_t block_tokens, int32_t num_kv_heads,
+                       int32_t head_dim, int32_t dtype, int32_t max_seqs,
+                       int32_t max_blocks_per_seq, gqa_kv_pool** out);
+void gqa_kv_pool_destroy(gqa_kv_pool* pool);
+int gqa_kv_pool_layout(const gqa_kv_pool* pool, gqa_kv_layout* out);
+/* Grows sequence `seq` to hold `num_tokens` tokens, taking blocks from the free list. */
+int gqa_kv_pool_reserve(gqa_kv_pool* pool, int32_t seq, int32_t num_tokens);
+/* Returns every block of `seq` to the free list. */
+int gqa_kv_pool_release(gqa_kv_pool* pool, int32_t seq);
+int32_t gqa_kv_pool_free_blocks(const gqa_kv_pool* pool);
+int32_t gqa_kv_pool_seq_blocks(const gqa_kv_pool* pool, int32_t seq);
+/* Host block table [max_seqs, max_blocks_per_seq] (-1 = unassigned); copy it to the device. */
+const int32_t* gqa_kv_pool_block_table(const gqa_kv_pool* pool);
+
+/* ---- KV-head-parallel partition -------------------------------------------------------- */
+/*
+ * New with respect to the reference, which runs on one device
+ * (code/source/model/qwen3_fused.cpp:68): rank r of n owns kv heads
+ * [first_kv_head, first_kv_head + num_local_kv_heads) together with their query groups.
+ * n must divide num_kv_heads.
+ */
+int gqa_shard_plan(int32_t num_q_heads, int32_t num_kv_heads, int32_t nranks, int32_t rank,
+                   int32_t* first_kv_head, int32_t* num_local_kv_heads,
+                   int32_t* first_q_head, int32_t* num_local_q_heads);
+
+#define GQA_COMM_ID_BYTES 128
+typedef struct gqa_comm gqa_comm;
+
+int32_t gqa_comm_nranks(const gqa_comm* comm);
+/* All-gather of `bytes` bytes per rank on `stream`; recv is [nranks][bytes]. */
+int gqa_comm_all_gather(gqa_comm* comm, const void* send, void* recv, size_t bytes, void* stream);
+
+/* Rank 0 makes the id; the caller hands it to every rank (any host channel). */
+int gqa_comm_unique_id(void* id_out);
+/* Collective over all ranks; the current CUDA device is the rank's GPU. */
+int gqa_comm_init(const void* id, int32_t nranks, int32_t rank, gqa_comm** out);
+void gqa_comm_destroy(gqa_comm* comm);
+
+/*
+ * Runs gqa_decode on this rank's heads (p describes the LOCAL shard: local head counts,
+ * local caches) and gathers every rank's output over NVLink with one ncclAllGather on
+ * p->stream. p->out is the local output [batch, local_q_heads, head_dim]; gathered is
+ * [nranks, batch, local_q_heads, head_dim].
+ */
+int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathered);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GQA_B200_H */

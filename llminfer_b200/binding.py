@@ -1,0 +1,477 @@
+"""ctypes binding of ``libgqa_b200.so`` (the C ABI in ``include/gqa_b200.h``).
+
+Tensors are ``torch`` tensors used only as owners of device memory: every call passes raw
+``data_ptr()`` values and sizes across the C ABI. There is no fallback path: if the library
+has not been built, importing it raises; if a call fails, ``GqaError`` carries the status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Optional, Sequence
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libgqa_b200.so"
+
+DTYPE_F32 = 1
+DTYPE_BF16 = 2
+CHUNK_KEYS = 32
+COMM_ID_BYTES = 128
+
+
+class GqaError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        super().__init__(f"{where}: status {status} ({status_string(status)})")
+
+
+class _Layout(C.Structure):
+    _fields_ = [
+        ("block_tokens", C.c_int32),
+        ("num_blocks", C.c_int32),
+        ("stride_block", C.c_int64),
+        ("stride_token", C.c_int64),
+        ("stride_head", C.c_int64),
+    ]
+
+
+class _DecodeParams(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int32),
+        ("batch", C.c_int32),
+        ("num_q_heads", C.c_int32),
+        ("num_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("blocks_per_seq", C.c_int32),
+        ("fixed_block", C.c_int32),
+        ("split_keys", C.c_int32),
+        ("max_ctas", C.c_int32),
+        ("plan_len_hint", C.c_int32),
+        ("layout", _Layout),
+        ("q", C.c_void_p),
+        ("k_cache", C.c_void_p),
+        ("v_cache", C.c_void_p),
+        ("out", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+        ("seq_lens_host", C.POINTER(C.c_int32)),
+        ("seq_lens_dev", C.c_void_p),
+        ("block_table_dev", C.c_void_p),
+        ("status_dev", C.c_void_p),
+        ("stream", C.c_void_p),
+    ]
+
+
+class _PlanInfo(C.Structure):
+    _fields_ = [
+        ("split_chunks", C.c_int32),
+        ("max_splits", C.c_int32),
+        ("num_items", C.c_int32),
+        ("num_ctas", C.c_int32),
+        ("needs_combine", C.c_int32),
+        ("reserved", C.c_int32),
+        ("workspace_bytes", C.c_size_t),
+    ]
+
+
+class _FrontParams(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32),
+        ("num_q_heads", C.c_int32),
+        ("num_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("blocks_per_seq", C.c_int32),
+        ("fixed_block", C.c_int32),
+        ("table_len", C.c_int32),
+        ("eps", C.c_float),
+        ("layout", _Layout),
+        ("q", C.c_void_p),
+        ("q_out", C.c_void_p),
+        ("k_new", C.c_void_p),
+        ("v_new", C.c_void_p),
+        ("qk_weight", C.c_void_p),
+        ("k_cache", C.c_void_p),
+        ("v_cache", C.c_void_p),
+        ("sin_cache", C.c_void_p),
+        ("cos_cache", C.c_void_p),
+        ("positions_host", C.POINTER(C.c_int32)),
+        ("positions_dev", C.c_void_p),
+        ("block_table_dev", C.c_void_p),
+        ("stream", C.c_void_p),
+    ]
+
+
+# Every symbol include/gqa_b200.h declares, with its ctypes signature.
+_SIGNATURES = {
+    "gqa_status_string": (C.c_char_p, [C.c_int]),
+    "gqa_abi_version": (C.c_int, []),
+    "gqa_layout_reference": (C.c_int, [C.c_int32] * 4 + [C.POINTER(_Layout)]),
+    "gqa_layout_pool": (C.c_int, [C.c_int32] * 4 + [C.POINTER(_Layout)]),
+    "gqa_decode_plan": (C.c_int, [C.POINTER(_DecodeParams), C.c_int32, C.POINTER(_PlanInfo)]),
+    "gqa_decode": (C.c_int, [C.POINTER(_DecodeParams)]),
+    "gqa_qk_norm_rope_append": (C.c_int, [C.POINTER(_FrontParams)]),
+    "gqa_sin_cos_cache": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "gqa_session_create": (C.c_int, [C.c_int32] * 6 + [C.POINTER(C.c_void_p)]),
+    "gqa_session_destroy": (None, [C.c_void_p]),
+    "gqa_session_step": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(_Layout),
+                                   C.POINTER(C.c_int32), C.c_void_p, C.c_int32, C.c_int32,
+                                   C.c_void_p]),
+    "gqa_session_step_sharded": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                           C.c_void_p, C.POINTER(_Layout), C.POINTER(C.c_int32),
+                                           C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "gqa_kv_pool_bytes": (C.c_size_t, [C.c_int32] * 5),
+    "gqa_kv_pool_create": (C.c_int, [C.c_int32] * 7 + [C.POINTER(C.c_void_p)]),
+    "gqa_kv_pool_destroy": (None, [C.c_void_p]),
+    "gqa_kv_pool_layout": (C.c_int, [C.c_void_p, C.POINTER(_Layout)]),
+    "gqa_kv_pool_reserve": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32]),
+    "gqa_kv_pool_release": (C.c_int, [C.c_void_p, C.c_int32]),
+    "gqa_kv_pool_free_blocks": (C.c_int32, [C.c_void_p]),
+    "gqa_kv_pool_seq_blocks": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "gqa_kv_pool_block_table": (C.POINTER(C.c_int32), [C.c_void_p]),
+    "gqa_shard_plan": (C.c_int, [C.c_int32] * 4 + [C.POINTER(C.c_int32)] * 4),
+    "gqa_comm_nranks": (C.c_int32, [C.c_void_p]),
+    "gqa_comm_all_gather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "gqa_comm_unique_id": (C.c_int, [C.c_void_p]),
+    "gqa_comm_init": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "gqa_comm_destroy": (None, [C.c_void_p]),
+    "gqa_decode_sharded": (C.c_int, [C.POINTER(_DecodeParams), C.c_void_p, C.c_void_p]),
+}
+
+_lib: Optional[C.CDLL] = None
+
+
+def lib() -> C.CDLL:
+    """Loads the CUDA library; raises if it was not built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise ImportError(
+                f"{_LIB_PATH} is missing: build it with `python -m llminfer_b200.build`; "
+                "there is no CPU or PyTorch fallback for this path")
+        handle = C.CDLL(str(_LIB_PATH), mode=C.RTLD_GLOBAL)
+        for name, (restype, argtypes) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def exported_symbols() -> Sequence[str]:
+    return tuple(_SIGNATURES)
+
+
+def status_string(status: int) -> str:
+    return lib().gqa_status_string(status).decode()
+
+
+def _check(status: int, where: str) -> None:
+    if status != 0:
+        raise GqaError(status, where)
+
+
+@dataclass(frozen=True)
+class KvLayout:
+    block_tokens: int
+    num_blocks: int
+    stride_block: int
+    stride_token: int
+    stride_head: int
+
+    def c(self) -> _Layout:
+        return _Layout(self.block_tokens, self.num_blocks, self.stride_block, self.stride_token,
+                       self.stride_head)
+
+    @staticmethod
+    def from_c(l: _Layout) -> "KvLayout":
+        return KvLayout(l.block_tokens, l.num_blocks, l.stride_block, l.stride_token,
+                        l.stride_head)
+
+
+def layout_reference(layer_num: int, max_seq_len: int, num_kv_heads: int,
+                     head_dim: int = 128) -> KvLayout:
+    out = _Layout()
+    _check(lib().gqa_layout_reference(layer_num, max_seq_len, num_kv_heads, head_dim,
+                                      C.byref(out)), "gqa_layout_reference")
+    return KvLayout.from_c(out)
+
+
+def layout_pool(num_blocks: int, block_tokens: int, num_kv_heads: int,
+                head_dim: int = 128) -> KvLayout:
+    out = _Layout()
+    _check(lib().gqa_layout_pool(num_blocks, block_tokens, num_kv_heads, head_dim, C.byref(out)),
+           "gqa_layout_pool")
+    return KvLayout.from_c(out)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return DTYPE_BF16
+    if t.dtype == torch.float32:
+        return DTYPE_F32
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _int_array(values: Optional[Sequence[int]]):
+    if values is None:
+        return None
+    return (C.c_int32 * len(values))(*[int(v) for v in values])
+
+
+def _decode_params(q, k_cache, v_cache, out, layout, seq_lens_host, seq_lens_dev, block_table,
+                   fixed_block, workspace, split_keys, max_ctas, plan_len_hint, status, stream,
+                   keep):
+    batch, hq, d = q.shape
+    p = _DecodeParams()
+    p.dtype = _dtype_code(q)
+    p.batch, p.num_q_heads, p.head_dim = batch, hq, d
+    p.num_kv_heads = keep["num_kv_heads"]
+    p.blocks_per_seq = 0 if block_table is None else block_table.shape[1]
+    p.fixed_block = fixed_block
+    p.split_keys = split_keys
+    p.max_ctas = max_ctas
+    p.plan_len_hint = plan_len_hint
+    p.layout = layout.c()
+    p.q, p.k_cache, p.v_cache, p.out = _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out)
+    p.workspace = _ptr(workspace)
+    p.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    lens = _int_array(seq_lens_host)
+    keep["lens"] = lens
+    p.seq_lens_host = lens
+    p.seq_lens_dev = _ptr(seq_lens_dev)
+    p.block_table_dev = _ptr(block_table)
+    p.status_dev = _ptr(status)
+    p.stream = stream
+    return p
+
+
+def decode_plan(*, dtype: int, batch: int, num_q_heads: int, num_kv_heads: int, layout: KvLayout,
+                seq_lens: Optional[Sequence[int]], blocks_per_seq: int = 0, fixed_block: int = 0,
+                split_keys: int = 0, max_ctas: int = 0, plan_len_hint: int = 0,
+                workspace_bytes: int = 0, sm_count: int = 148, paged: bool = False,
+                device_lens: bool = False, head_dim: int = 128) -> dict:
+    """Host-only split planning (no device memory is touched; pointers are placeholders)."""
+    p = _DecodeParams()
+    p.dtype, p.batch, p.num_q_heads, p.num_kv_heads, p.head_dim = (
+        dtype, batch, num_q_heads, num_kv_heads, head_dim)
+    p.blocks_per_seq, p.fixed_block = blocks_per_seq, fixed_block
+    p.split_keys, p.max_ctas, p.plan_len_hint = split_keys, max_ctas, plan_len_hint
+    p.layout = layout.c()
+    fake = 0x1000  # validation only looks at nullness and alignment
+    p.q = p.k_cache = p.v_cache = p.out = fake
+    p.workspace = fake if workspace_bytes else None
+    p.workspace_bytes = workspace_bytes
+    lens = _int_array(seq_lens)
+    p.seq_lens_host = lens
+    p.seq_lens_dev = fake if device_lens else None
+    p.block_table_dev = fake if paged else None
+    info = _PlanInfo()
+    _check(lib().gqa_decode_plan(C.byref(p), sm_count, C.byref(info)), "gqa_decode_plan")
+    return {f: getattr(info, f) for f, _ in _PlanInfo._fields_ if f != "reserved"}
+
+
+def decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, *,
+           num_kv_heads: int, layout: KvLayout, seq_lens: Optional[Sequence[int]] = None,
+           seq_lens_dev: Optional[torch.Tensor] = None,
+           block_table: Optional[torch.Tensor] = None, fixed_block: int = 0,
+           workspace: Optional[torch.Tensor] = None, split_keys: int = 0, max_ctas: int = 0,
+           plan_len_hint: int = 0, status: Optional[torch.Tensor] = None,
+           stream: Optional[int] = None) -> None:
+    """Decode attention for q [batch, num_q_heads, 128] on the current stream (or `stream`)."""
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    keep = {"num_kv_heads": num_kv_heads}
+    p = _decode_params(q, k_cache, v_cache, out, layout, seq_lens, seq_lens_dev, block_table,
+                       fixed_block, workspace, split_keys, max_ctas, plan_len_hint, status,
+                       stream, keep)
+    _check(lib().gqa_decode(C.byref(p)), "gqa_decode")
+
+
+def workspace_for(batch: int, num_q_heads: int, num_kv_heads: int, device,
+                  sm_count: int = 148) -> torch.Tensor:
+    """A scratch tensor large enough for any plan the library may pick for this shape."""
+    group = num_q_heads // num_kv_heads
+    records = 16 * sm_count + 2 * batch * num_kv_heads
+    return torch.empty(records * group * 130, dtype=torch.float32, device=device)
+
+
+def qk_norm_rope_append(q: torch.Tensor, k_new: torch.Tensor, v_new: Optional[torch.Tensor],
+                        qk_weight: torch.Tensor, k_cache: torch.Tensor,
+                        v_cache: Optional[torch.Tensor], *, layout: KvLayout,
+                        positions: Optional[Sequence[int]] = None,
+                        positions_dev: Optional[torch.Tensor] = None,
+                        q_out: Optional[torch.Tensor] = None,
+                        sin_cache: Optional[torch.Tensor] = None,
+                        cos_cache: Optional[torch.Tensor] = None,
+                        block_table: Optional[torch.Tensor] = None, fixed_block: int = 0,
+                        eps: float = 1e-6, stream: Optional[int] = None) -> None:
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    batch, hq, d = q.shape
+    f = _FrontParams()
+    f.batch, f.num_q_heads, f.num_kv_heads, f.head_dim = batch, hq, k_new.shape[1], d
+    f.blocks_per_seq = 0 if block_table is None else block_table.shape[1]
+    f.fixed_block = fixed_block
+    f.table_len = 0 if sin_cache is None else sin_cache.shape[0]
+    f.eps = eps
+    f.layout = layout.c()
+    f.q = _ptr(q)
+    f.q_out = _ptr(q if q_out is None else q_out)
+    f.k_new, f.v_new, f.qk_weight = _ptr(k_new), _ptr(v_new), _ptr(qk_weight)
+    f.k_cache, f.v_cache = _ptr(k_cache), _ptr(v_cache)
+    f.sin_cache, f.cos_cache = _ptr(sin_cache), _ptr(cos_cache)
+    pos = _int_array(positions)
+    f.positions_host = pos
+    f.positions_dev = _ptr(positions_dev)
+    f.block_table_dev = _ptr(block_table)
+    f.stream = stream
+    _check(lib().gqa_qk_norm_rope_append(C.byref(f)), "gqa_qk_norm_rope_append")
+
+
+def sin_cos_cache(sin_cache: torch.Tensor, cos_cache: torch.Tensor, head_dim: int,
+                  stream: Optional[int] = None) -> None:
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    _check(lib().gqa_sin_cos_cache(_ptr(sin_cache), _ptr(cos_cache), head_dim,
+                                   sin_cache.shape[0], stream), "gqa_sin_cos_cache")
+
+
+class Session:
+    """Decode steps from host buffers (H2D of the new rows, kernels, D2H of the output)."""
+
+    def __init__(self, max_batch: int, num_q_heads: int, num_kv_heads: int, max_seq_len: int,
+                 head_dim: int = 128):
+        self._h = C.c_void_p()
+        _check(lib().gqa_session_create(DTYPE_BF16, max_batch, num_q_heads, num_kv_heads,
+                                        head_dim, max_seq_len, C.byref(self._h)),
+               "gqa_session_create")
+
+    def step(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
+             qk_weight: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+             layout: KvLayout, positions: Sequence[int], out_host: torch.Tensor,
+             block_table: Optional[torch.Tensor] = None, fixed_block: int = 0,
+             comm: Optional["ShardComm"] = None) -> None:
+        """With `comm`, out_host is the gathered [nranks, batch, local_q_heads, 128] output."""
+        lay = layout.c()
+        pos = _int_array(positions)
+        bps = 0 if block_table is None else block_table.shape[1]
+        if comm is None:
+            _check(lib().gqa_session_step(self._h, q_host.shape[0], _ptr(q_host), _ptr(k_host),
+                                          _ptr(v_host), _ptr(qk_weight), _ptr(k_cache),
+                                          _ptr(v_cache), C.byref(lay), pos, _ptr(block_table),
+                                          bps, fixed_block, _ptr(out_host)), "gqa_session_step")
+        else:
+            _check(lib().gqa_session_step_sharded(
+                self._h, comm._h, q_host.shape[0], _ptr(q_host), _ptr(k_host), _ptr(v_host),
+                _ptr(qk_weight), _ptr(k_cache), _ptr(v_cache), C.byref(lay), pos,
+                _ptr(block_table), bps, fixed_block, _ptr(out_host)), "gqa_session_step_sharded")
+
+    def close(self) -> None:
+        if self._h:
+            lib().gqa_session_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class KvPool:
+    """Host-side block pool; `table()` returns the [max_seqs, max_blocks_per_seq] block table."""
+
+    def __init__(self, num_blocks: int, block_tokens: int, num_kv_heads: int, max_seqs: int,
+                 max_blocks_per_seq: int, dtype: int = DTYPE_BF16, head_dim: int = 128):
+        self._h = C.c_void_p()
+        self.max_seqs, self.max_blocks_per_seq = max_seqs, max_blocks_per_seq
+        self.bytes = lib().gqa_kv_pool_bytes(num_blocks, block_tokens, num_kv_heads, head_dim,
+                                             dtype)
+        _check(lib().gqa_kv_pool_create(num_blocks, block_tokens, num_kv_heads, head_dim, dtype,
+                                        max_seqs, max_blocks_per_seq, C.byref(self._h)),
+               "gqa_kv_pool_create")
+
+    def layout(self) -> KvLayout:
+        out = _Layout()
+        _check(lib().gqa_kv_pool_layout(self._h, C.byref(out)), "gqa_kv_pool_layout")
+        return KvLayout.from_c(out)
+
+    def reserve(self, seq: int, num_tokens: int) -> None:
+        _check(lib().gqa_kv_pool_reserve(self._h, seq, num_tokens), "gqa_kv_pool_reserve")
+
+    def release(self, seq: int) -> None:
+        _check(lib().gqa_kv_pool_release(self._h, seq), "gqa_kv_pool_release")
+
+    def free_blocks(self) -> int:
+        return lib().gqa_kv_pool_free_blocks(self._h)
+
+    def seq_blocks(self, seq: int) -> int:
+        return lib().gqa_kv_pool_seq_blocks(self._h, seq)
+
+    def table(self) -> torch.Tensor:
+        ptr = lib().gqa_kv_pool_block_table(self._h)
+        n = self.max_seqs * self.max_blocks_per_seq
+        flat = [ptr[i] for i in range(n)]
+        return torch.tensor(flat, dtype=torch.int32).view(self.max_seqs, self.max_blocks_per_seq)
+
+    def close(self) -> None:
+        if self._h:
+            lib().gqa_kv_pool_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def shard_plan(num_q_heads: int, num_kv_heads: int, nranks: int, rank: int) -> dict:
+    vals = [C.c_int32() for _ in range(4)]
+    _check(lib().gqa_shard_plan(num_q_heads, num_kv_heads, nranks, rank,
+                                *[C.byref(v) for v in vals]), "gqa_shard_plan")
+    names = ("first_kv_head", "num_local_kv_heads", "first_q_head", "num_local_q_heads")
+    return {n: v.value for n, v in zip(names, vals)}
+
+
+class ShardComm:
+    """NCCL communicator owned by the library (one per process / GPU)."""
+
+    def __init__(self, unique_id: bytes, nranks: int, rank: int):
+        self._h = C.c_void_p()
+        buf = C.create_string_buffer(unique_id, COMM_ID_BYTES)
+        _check(lib().gqa_comm_init(buf, nranks, rank, C.byref(self._h)), "gqa_comm_init")
+        self.nranks, self.rank = nranks, rank
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(COMM_ID_BYTES)
+        _check(lib().gqa_comm_unique_id(buf), "gqa_comm_unique_id")
+        return buf.raw
+
+    def close(self) -> None:
+        if self._h:
+            lib().gqa_comm_destroy(self._h)
+            self._h = C.c_void_p()
+
+
+def decode_sharded(comm: ShardComm, gathered: torch.Tensor, q, k_cache, v_cache, out, *,
+                   num_kv_heads: int, layout: KvLayout, **kw) -> None:
+    """Local decode on this rank's heads followed by the all-gather into `gathered`."""
+    stream = kw.pop("stream", None)
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    keep = {"num_kv_heads": num_kv_heads}
+    p = _decode_params(q, k_cache, v_cache, out, layout, kw.get("seq_lens"),
+                       kw.get("seq_lens_dev"), kw.get("block_table"), kw.get("fixed_block", 0),
+                       kw.get("workspace"), kw.get("split_keys", 0), kw.get("max_ctas", 0),
+                       kw.get("plan_len_hint", 0), kw.get("status"), stream, keep)
+    _check(lib().gqa_decode_sharded(C.byref(p), comm._h, _ptr(gathered)), "gqa_decode_sharded")

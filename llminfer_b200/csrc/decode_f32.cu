@@ -1,0 +1,243 @@
+// FP32 decode attention (FP32 q / cache / output) and the LSE combine kernel.
+//
+// The FP32 kernel covers what the reference's CPU backend computes in FP32
+// (code/source/op/kernel/cpu/mha_kernel.cpp:34-110) and its op tests compare at 1e-5
+// (test/test_op/test_op_mha.cpp:62): scores, softmax and the weighted sum all stay in FP32 on
+// CUDA cores, with accurate exp2f. It uses the same item decomposition and partial-record
+// format as the BF16 kernel, so one combine kernel serves both. It is a parity path for
+// short FP32 caches, not a bandwidth path.
+//
+// The combine kernel takes the place of flashdecoding_gqa_combine_kernel
+// (code/source/op/kernel/cuda/mha_kernel.cu:399-438): out = sum_s O_s 2^(m_s - M) /
+// sum_s l_s 2^(m_s - M), splits merged in ascending order.
+#include "decode_kernels.cuh"
+#include "ptx.cuh"
+#include "work_map.cuh"
+
+namespace gqa {
+
+namespace {
+
+constexpr int kF32Warps = 4;
+constexpr int kF32Threads = kF32Warps * 32;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+    return v;
+}
+
+__device__ __forceinline__ const float* cache_row(const DecodeArgs& a, const void* base,
+                                                  int32_t b, int32_t hk, int32_t t) {
+    int32_t blk = a.fixed_block;
+    int32_t tok = t;
+    if (a.block_table != nullptr) {
+        const int32_t lb = t / a.block_tokens;
+        tok = t - lb * a.block_tokens;
+        blk = __ldg(a.block_table + (int64_t)b * a.blocks_per_seq + lb);
+    }
+    return reinterpret_cast<const float*>(base) + (int64_t)blk * a.stride_block +
+           (int64_t)tok * a.stride_token + (int64_t)hk * a.stride_head;
+}
+
+}  // namespace
+
+// G: query heads per kv head handled per pass (group <= G).
+template <int G>
+__global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const DecodeArgs a) {
+    __shared__ float s_o[kF32Warps][G][kHeadDim];
+    __shared__ float s_m[kF32Warps][G];
+    __shared__ float s_l[kF32Warps][G];
+    extern __shared__ int32_t s_tables[];
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const WorkTables tables = build_work_tables(a, s_tables);
+    const int32_t n_items = total_items(a, tables);
+    const int32_t group = a.group;
+
+    for (int32_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+        const Item it = decode_item(a, tables, item);
+
+        float4 q[G];
+        float m[G], l[G];
+        float4 o[G];
+#pragma unroll
+        for (int n = 0; n < G; ++n) {
+            q[n] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (n < group) {
+                q[n] = __ldg(reinterpret_cast<const float4*>(
+                                 reinterpret_cast<const float*>(a.q) +
+                                 ((int64_t)it.b * a.num_q_heads + (int64_t)it.hk * group + n) *
+                                     kHeadDim) + lane);
+            }
+            m[n] = -INFINITY;
+            l[n] = 0.f;
+            o[n] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+
+        for (int32_t k = it.chunk_begin + warp; k < it.chunk_end; k += kF32Warps) {
+            const int32_t t0 = k * kChunkKeys;
+            const int32_t valid = min(kChunkKeys, it.len - t0);
+
+            // Scores: lane j ends up holding the G scores of key t0 + j.
+            float sc[G];
+#pragma unroll
+            for (int n = 0; n < G; ++n) sc[n] = -INFINITY;
+            for (int32_t j0 = 0; j0 < valid; j0 += 4) {
+                float4 kv[4];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    kv[jj] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (j0 + jj < valid) {
+                        kv[jj] = __ldg(reinterpret_cast<const float4*>(
+                                           cache_row(a, a.k_cache, it.b, it.hk, t0 + j0 + jj)) + lane);
+                    }
+                }
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+#pragma unroll
+                    for (int n = 0; n < G; ++n) {
+                        float part = q[n].x * kv[jj].x + q[n].y * kv[jj].y + q[n].z * kv[jj].z +
+                                     q[n].w * kv[jj].w;
+                        part = warp_sum(part);
+                        if (lane == j0 + jj) sc[n] = part * a.scale_log2;
+                    }
+                }
+            }
+
+            float p[G];
+#pragma unroll
+            for (int n = 0; n < G; ++n) {
+                const float cmax = warp_max(sc[n]);
+                const float mnew = fmaxf(m[n], cmax);
+                const float alpha = exp2f(m[n] - mnew);
+                p[n] = (lane < valid) ? exp2f(sc[n] - mnew) : 0.f;
+                l[n] = l[n] * alpha + p[n];
+                o[n].x *= alpha; o[n].y *= alpha; o[n].z *= alpha; o[n].w *= alpha;
+                m[n] = mnew;
+            }
+
+            for (int32_t j = 0; j < valid; ++j) {
+                const float4 vv = __ldg(reinterpret_cast<const float4*>(
+                                            cache_row(a, a.v_cache, it.b, it.hk, t0 + j)) + lane);
+#pragma unroll
+                for (int n = 0; n < G; ++n) {
+                    const float pj = __shfl_sync(0xffffffffu, p[n], j);
+                    o[n].x += pj * vv.x; o[n].y += pj * vv.y;
+                    o[n].z += pj * vv.z; o[n].w += pj * vv.w;
+                }
+            }
+        }
+
+#pragma unroll
+        for (int n = 0; n < G; ++n) {
+            const float lt = warp_sum(l[n]);
+            if (lane == 0) {
+                s_m[warp][n] = m[n];
+                s_l[warp][n] = lt;
+            }
+            reinterpret_cast<float4*>(&s_o[warp][n][0])[lane] = o[n];
+        }
+        __syncthreads();
+        {
+            const bool final_out = (it.nsplits == 1);
+            float* rec = a.workspace + (int64_t)item * group * (kHeadDim + 2);
+            float* out = reinterpret_cast<float*>(a.out) +
+                ((int64_t)it.b * a.num_q_heads + (int64_t)it.hk * group) * kHeadDim;
+            for (int idx = threadIdx.x; idx < group * kHeadDim; idx += kF32Threads) {
+                const int n = idx >> 7;
+                const int d = idx & (kHeadDim - 1);
+                float mx = s_m[0][n];
+#pragma unroll
+                for (int w = 1; w < kF32Warps; ++w) mx = fmaxf(mx, s_m[w][n]);
+                float acc = 0.f, lsum = 0.f;
+#pragma unroll
+                for (int w = 0; w < kF32Warps; ++w) {
+                    const float f = exp2f(s_m[w][n] - mx);
+                    acc += s_o[w][n][d] * f;
+                    lsum += s_l[w][n] * f;
+                }
+                if (final_out) {
+                    out[idx] = acc / lsum;
+                } else {
+                    rec[idx] = acc;
+                    if (d == 0) {
+                        rec[group * kHeadDim + n] = mx;
+                        rec[group * kHeadDim + group + n] = lsum;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <bool BF16_OUT>
+__global__ void __launch_bounds__(kHeadDim) gqa_decode_combine(const DecodeArgs a) {
+    extern __shared__ int32_t s_tables[];
+    const WorkTables tables = build_work_tables(a, s_tables);
+    const int32_t b = blockIdx.x / a.num_q_heads;
+    const int32_t h = blockIdx.x - b * a.num_q_heads;
+    const int32_t group = a.group;
+    const int32_t hk = h / group;
+    const int32_t n = h - hk * group;
+    int32_t first, nsplits;
+    unit_items(a, tables, b, hk, &first, &nsplits);
+    if (nsplits <= 1) return;  // the streaming kernel already wrote the final output
+
+    const int d = threadIdx.x;
+    const int64_t rec_floats = (int64_t)group * (kHeadDim + 2);
+    const float* rec0 = a.workspace + (int64_t)first * rec_floats;
+    float mx = -INFINITY;
+    for (int32_t s = 0; s < nsplits; ++s) {
+        mx = fmaxf(mx, rec0[s * rec_floats + group * kHeadDim + n]);
+    }
+    float acc = 0.f, lsum = 0.f;
+    for (int32_t s = 0; s < nsplits; ++s) {
+        const float* rec = rec0 + s * rec_floats;
+        const float ms = rec[group * kHeadDim + n];
+        const float f = BF16_OUT ? ex2_approx(ms - mx) : exp2f(ms - mx);
+        acc += rec[n * kHeadDim + d] * f;
+        lsum += rec[group * kHeadDim + group + n] * f;
+    }
+    const int64_t o_idx = ((int64_t)b * a.num_q_heads + h) * kHeadDim + d;
+    if (BF16_OUT) {
+        reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(acc / lsum);
+    } else {
+        reinterpret_cast<float*>(a.out)[o_idx] = acc / lsum;
+    }
+}
+
+cudaError_t launch_stream_f32(const DecodeArgs& args, int grid, cudaStream_t stream) {
+    const size_t smem =
+        args.seq_lens_dev != nullptr ? 2 * ((size_t)args.batch + 1) * sizeof(int32_t) : 0;
+    if (args.group <= 2) {
+        gqa_decode_stream_f32<2><<<grid, kF32Threads, smem, stream>>>(args);
+    } else if (args.group <= 4) {
+        gqa_decode_stream_f32<4><<<grid, kF32Threads, smem, stream>>>(args);
+    } else {
+        gqa_decode_stream_f32<8><<<grid, kF32Threads, smem, stream>>>(args);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t stream) {
+    const size_t smem =
+        args.seq_lens_dev != nullptr ? 2 * ((size_t)args.batch + 1) * sizeof(int32_t) : 0;
+    const int grid = args.batch * args.num_q_heads;
+    if (bf16_out) {
+        gqa_decode_combine<true><<<grid, kHeadDim, smem, stream>>>(args);
+    } else {
+        gqa_decode_combine<false><<<grid, kHeadDim, smem, stream>>>(args);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace gqa

@@ -1,0 +1,550 @@
+// C ABI of the decode-attention library: validation, split planning, tensor-map set-up and
+// kernel launches. See include/gqa_b200.h for the contract of every entry point.
+#include "../../include/gqa_b200.h"
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include "decode_kernels.cuh"
+#include "work_map.cuh"
+
+namespace {
+
+using gqa::ceil_div;
+using gqa::kChunkKeys;
+using gqa::kHeadDim;
+
+constexpr int kMaxGroup = 8;
+constexpr int kPlanWarps = 4;  // warps sharing an item in both streaming kernels
+
+size_t dtype_bytes(int32_t dtype) { return dtype == GQA_DTYPE_F32 ? 4 : 2; }
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int validate_layout(const gqa_kv_layout& l, int32_t dtype, int32_t num_kv_heads) {
+    if (l.block_tokens <= 0 || l.num_blocks <= 0) return GQA_ERR_SHAPE;
+    if (l.stride_block <= 0 || l.stride_token <= 0 || l.stride_head <= 0) return GQA_ERR_SHAPE;
+    const int64_t eb = (int64_t)dtype_bytes(dtype);
+    if ((l.stride_block * eb) % 16 || (l.stride_token * eb) % 16 || (l.stride_head * eb) % 16) {
+        return GQA_ERR_ALIGN;
+    }
+    if (l.stride_head < kHeadDim && num_kv_heads > 1) return GQA_ERR_SHAPE;
+    return GQA_OK;
+}
+
+// Everything that can be checked without touching device memory.
+int validate_decode(const gqa_decode_params* p) {
+    if (p == nullptr) return GQA_ERR_NULL;
+    if (p->dtype != GQA_DTYPE_F32 && p->dtype != GQA_DTYPE_BF16) return GQA_ERR_DTYPE;
+    if (p->batch <= 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0) return GQA_ERR_SHAPE;
+    if (p->head_dim != kHeadDim) return GQA_ERR_SHAPE;
+    if (p->num_q_heads % p->num_kv_heads != 0) return GQA_ERR_SHAPE;
+    if (p->num_q_heads / p->num_kv_heads > kMaxGroup) return GQA_ERR_UNSUPPORTED;
+    int rc = validate_layout(p->layout, p->dtype, p->num_kv_heads);
+    if (rc != GQA_OK) return rc;
+    if (p->q == nullptr || p->k_cache == nullptr || p->v_cache == nullptr || p->out == nullptr) {
+        return GQA_ERR_NULL;
+    }
+    if (!aligned16(p->q) || !aligned16(p->k_cache) || !aligned16(p->v_cache) ||
+        !aligned16(p->out)) {
+        return GQA_ERR_ALIGN;
+    }
+    if (p->seq_lens_host == nullptr && p->seq_lens_dev == nullptr) return GQA_ERR_NULL;
+    if (p->split_keys < 0 || p->max_ctas < 0 || p->plan_len_hint < 0) return GQA_ERR_RANGE;
+    int64_t capacity;  // tokens one sequence can hold
+    if (p->block_table_dev != nullptr) {
+        if (p->blocks_per_seq <= 0) return GQA_ERR_SHAPE;
+        if (p->blocks_per_seq > 1 && p->layout.block_tokens % kChunkKeys != 0) return GQA_ERR_SHAPE;
+        capacity = (int64_t)p->blocks_per_seq * p->layout.block_tokens;
+    } else {
+        if (p->batch != 1) return GQA_ERR_SHAPE;
+        if (p->fixed_block < 0 || p->fixed_block >= p->layout.num_blocks) return GQA_ERR_RANGE;
+        capacity = p->layout.block_tokens;
+    }
+    if (p->seq_lens_host != nullptr) {
+        for (int32_t b = 0; b < p->batch; ++b) {
+            const int32_t len = p->seq_lens_host[b];
+            if (len <= 0 || len > capacity) return GQA_ERR_RANGE;
+            if (p->seq_lens_dev == nullptr && len != p->seq_lens_host[0]) return GQA_ERR_UNSUPPORTED;
+        }
+    } else if (p->batch > gqa::kMaxRaggedBatch) {
+        return GQA_ERR_UNSUPPORTED;
+    }
+    if (p->seq_lens_dev != nullptr && p->batch > gqa::kMaxRaggedBatch) return GQA_ERR_UNSUPPORTED;
+    if (p->plan_len_hint > capacity) return GQA_ERR_RANGE;
+    return GQA_OK;
+}
+
+int device_sm_count(int32_t* out) {
+    static std::mutex mu;
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return GQA_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) {
+        *out = cached[dev];
+        return GQA_OK;
+    }
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        sms <= 0) {
+        return GQA_ERR_CUDA;
+    }
+    if (dev >= 0 && dev < 64) cached[dev] = sms;
+    *out = sms;
+    return GQA_OK;
+}
+
+// ---- split planning ------------------------------------------------------------------------
+// Cost of a candidate, in "steps": one step is every warp of a CTA consuming one chunk.
+// A CTA runs its items back to back (its copies run ahead across items), each item ends with
+// a merge of the warps; a split unit additionally pays the combine launch.
+constexpr double kItemOverhead = 1.0;
+constexpr double kCombineBase = 3.0;
+constexpr double kCombinePerSplit = 0.05;
+
+struct PlanInput {
+    int32_t batch;
+    int32_t num_kv_heads;
+    int32_t group;
+    const int32_t* lens;  // host lengths or null
+    int32_t uniform_len;  // used when lens is null
+    int32_t sm_count;
+    int32_t max_ctas;
+    int32_t split_keys;
+    size_t workspace_bytes;  // 0 = unconstrained
+};
+
+int64_t items_for(const PlanInput& in, int32_t q, int32_t* max_splits) {
+    int64_t items = 0;
+    int32_t ms = 0;
+    for (int32_t b = 0; b < in.batch; ++b) {
+        const int32_t len = in.lens ? in.lens[b] : in.uniform_len;
+        const int32_t s = ceil_div(ceil_div(len, kChunkKeys), q);
+        items += (int64_t)s * in.num_kv_heads;
+        ms = s > ms ? s : ms;
+        if (!in.lens) {
+            items *= in.batch;
+            break;
+        }
+    }
+    *max_splits = ms;
+    return items;
+}
+
+size_t record_bytes(int32_t group) { return (size_t)group * (kHeadDim + 2) * sizeof(float); }
+
+int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
+    int32_t max_chunks = 0;
+    for (int32_t b = 0; b < in.batch; ++b) {
+        const int32_t len = in.lens ? in.lens[b] : in.uniform_len;
+        const int32_t c = ceil_div(len, kChunkKeys);
+        max_chunks = c > max_chunks ? c : max_chunks;
+        if (!in.lens) break;
+    }
+    const int32_t g_max = in.max_ctas > 0 && in.max_ctas < in.sm_count ? in.max_ctas : in.sm_count;
+    const size_t rec = record_bytes(in.group);
+
+    auto finish = [&](int32_t q) -> int {
+        int32_t ms = 0;
+        const int64_t items = items_for(in, q, &ms);
+        if (items > INT32_MAX) return GQA_ERR_SHAPE;
+        out->split_chunks = q;
+        out->max_splits = ms;
+        out->num_items = (int32_t)items;
+        out->num_ctas = (int32_t)(items < g_max ? items : g_max);
+        out->needs_combine = ms > 1 ? 1 : 0;
+        out->reserved = 0;
+        out->workspace_bytes = ms > 1 ? (size_t)items * rec : 0;
+        if (in.workspace_bytes != 0 && out->workspace_bytes > in.workspace_bytes) {
+            return GQA_ERR_WORKSPACE;
+        }
+        return GQA_OK;
+    };
+
+    if (in.split_keys > 0) return finish(ceil_div(in.split_keys, kChunkKeys));
+
+    // Candidates: q = ceil(max_chunks / s) for s = 1, 2, ... while the grid is not yet
+    // oversubscribed eight times; evaluated with the uniform upper bound on item size.
+    double best_cost = 0.0;
+    int32_t best_q = max_chunks;
+    bool have = false;
+    int32_t last_q = -1;
+    for (int32_t s = 1; s <= max_chunks; ++s) {
+        const int32_t q = ceil_div(max_chunks, s);
+        if (q == last_q) continue;
+        last_q = q;
+        int32_t ms = 0;
+        const int64_t items = items_for(in, q, &ms);
+        if (in.workspace_bytes != 0 && ms > 1 && (size_t)items * rec > in.workspace_bytes) break;
+        const int64_t rounds = (items + g_max - 1) / g_max;
+        double cost = (double)rounds * ((double)ceil_div(q, kPlanWarps) + kItemOverhead);
+        if (ms > 1) cost += kCombineBase + kCombinePerSplit * ms;
+        if (!have || cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best_q = q;
+            have = true;
+        }
+        if (items > (int64_t)8 * g_max) break;
+    }
+    if (!have) return GQA_ERR_WORKSPACE;
+    return finish(best_q);
+}
+
+int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out) {
+    PlanInput in;
+    in.batch = p->batch;
+    in.num_kv_heads = p->num_kv_heads;
+    in.group = p->num_q_heads / p->num_kv_heads;
+    in.lens = p->seq_lens_host;
+    in.uniform_len = 0;
+    if (in.lens == nullptr) {
+        const int64_t capacity = p->block_table_dev != nullptr
+                                     ? (int64_t)p->blocks_per_seq * p->layout.block_tokens
+                                     : p->layout.block_tokens;
+        in.uniform_len = p->plan_len_hint > 0 ? p->plan_len_hint : (int32_t)capacity;
+    }
+    in.sm_count = sm_count;
+    in.max_ctas = p->max_ctas;
+    in.split_keys = p->split_keys;
+    in.workspace_bytes = p->workspace != nullptr ? p->workspace_bytes : 0;
+    int rc = make_plan(in, out);
+    if (rc != GQA_OK) return rc;
+    if (p->seq_lens_host == nullptr) {
+        // Lengths are only known on the device: size the scratch for full sequences.
+        PlanInput full = in;
+        const int64_t capacity = p->block_table_dev != nullptr
+                                     ? (int64_t)p->blocks_per_seq * p->layout.block_tokens
+                                     : p->layout.block_tokens;
+        full.uniform_len = (int32_t)capacity;
+        full.split_keys = out->split_chunks * kChunkKeys;
+        gqa_decode_plan_info upper;
+        rc = make_plan(full, &upper);
+        if (rc != GQA_OK) return rc;
+        out->num_items = upper.num_items;
+        out->max_splits = upper.max_splits;
+        out->needs_combine = upper.needs_combine;
+        out->workspace_bytes = upper.workspace_bytes;
+        const int32_t g_max = in.max_ctas > 0 && in.max_ctas < sm_count ? in.max_ctas : sm_count;
+        out->num_ctas = upper.num_items < g_max ? upper.num_items : g_max;
+    }
+    return GQA_OK;
+}
+
+// ---- tensor maps ------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+                cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(sym);
+        }
+    });
+    return fn;
+}
+
+// BF16 cache as a rank-4 tensor (channel, then token/head by ascending stride, then block);
+// the box is one 64-channel half of a 32-key chunk of one head, swizzled in 128-byte rows.
+int encode_cache_map(const void* base, const gqa_kv_layout& l, int32_t num_kv_heads,
+                     bool* head_before_token, CUtensorMap* map) {
+    auto fn = encode_fn();
+    if (fn == nullptr) return GQA_ERR_CUDA;
+    const bool head_first = l.stride_head < l.stride_token;
+    *head_before_token = head_first;
+    cuuint64_t dims[4];
+    cuuint64_t strides[3];
+    cuuint32_t box[4];
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    dims[0] = kHeadDim;
+    box[0] = 64;
+    if (head_first) {
+        dims[1] = (cuuint64_t)num_kv_heads;
+        strides[0] = (cuuint64_t)l.stride_head * 2;
+        box[1] = 1;
+        dims[2] = (cuuint64_t)l.block_tokens;
+        strides[1] = (cuuint64_t)l.stride_token * 2;
+        box[2] = kChunkKeys;
+    } else {
+        dims[1] = (cuuint64_t)l.block_tokens;
+        strides[0] = (cuuint64_t)l.stride_token * 2;
+        box[1] = kChunkKeys;
+        dims[2] = (cuuint64_t)num_kv_heads;
+        strides[1] = (cuuint64_t)l.stride_head * 2;
+        box[2] = 1;
+    }
+    dims[3] = (cuuint64_t)l.num_blocks;
+    strides[2] = (cuuint64_t)l.stride_block * 2;
+    box[3] = 1;
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? GQA_OK : GQA_ERR_UNSUPPORTED;
+}
+
+// Encoding costs a few microseconds; decode steps reuse the same caches, so keep the last few.
+struct MapCacheEntry {
+    const void* base;
+    gqa_kv_layout layout;
+    int32_t heads;
+    bool head_first;
+    CUtensorMap map;
+};
+
+int cached_cache_map(const void* base, const gqa_kv_layout& l, int32_t heads, bool* head_first,
+                     CUtensorMap* map) {
+    static std::mutex mu;
+    static std::vector<MapCacheEntry> cache;
+    static size_t next = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    for (const auto& e : cache) {
+        if (e.base == base && e.heads == heads &&
+            std::memcmp(&e.layout, &l, sizeof(gqa_kv_layout)) == 0) {
+            *map = e.map;
+            *head_first = e.head_first;
+            return GQA_OK;
+        }
+    }
+    MapCacheEntry e;
+    std::memset(&e, 0, sizeof(e));
+    e.base = base;
+    e.layout = l;
+    e.heads = heads;
+    const int rc = encode_cache_map(base, l, heads, &e.head_first, &e.map);
+    if (rc != GQA_OK) return rc;
+    if (cache.size() < 32) {
+        cache.push_back(e);
+    } else {
+        cache[next] = e;
+        next = (next + 1) % cache.size();
+    }
+    *map = e.map;
+    *head_first = e.head_first;
+    return GQA_OK;
+}
+
+gqa_kv_layout clean_layout(const gqa_kv_layout& l) {
+    gqa_kv_layout c;
+    std::memset(&c, 0, sizeof(c));  // padding bytes take part in the cache key
+    c.block_tokens = l.block_tokens;
+    c.num_blocks = l.num_blocks;
+    c.stride_block = l.stride_block;
+    c.stride_token = l.stride_token;
+    c.stride_head = l.stride_head;
+    return c;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* gqa_status_string(int status) {
+    switch (status) {
+        case GQA_OK: return "ok";
+        case GQA_ERR_NULL: return "a required pointer is null";
+        case GQA_ERR_DTYPE: return "unsupported dtype";
+        case GQA_ERR_SHAPE: return "unsupported shape or layout";
+        case GQA_ERR_ALIGN: return "pointer or stride is not 16-byte aligned";
+        case GQA_ERR_RANGE: return "position or length outside the cache";
+        case GQA_ERR_WORKSPACE: return "workspace too small";
+        case GQA_ERR_CUDA: return "CUDA call failed or no device";
+        case GQA_ERR_UNSUPPORTED: return "request not covered by this build";
+        case GQA_ERR_COMM: return "NCCL missing or collective failed";
+        case GQA_ERR_POOL: return "KV pool error";
+        case GQA_ERR_TIMEOUT: return "bounded device wait ran out";
+        default: return "unknown status";
+    }
+}
+
+int gqa_abi_version(void) { return GQA_B200_ABI_VERSION; }
+
+int gqa_layout_reference(int32_t layer_num, int32_t max_seq_len, int32_t num_kv_heads,
+                         int32_t head_dim, gqa_kv_layout* out) {
+    if (out == nullptr) return GQA_ERR_NULL;
+    if (layer_num <= 0 || max_seq_len <= 0 || num_kv_heads <= 0 || head_dim <= 0) {
+        return GQA_ERR_SHAPE;
+    }
+    std::memset(out, 0, sizeof(*out));
+    out->block_tokens = max_seq_len;
+    out->num_blocks = layer_num;
+    out->stride_head = head_dim;
+    out->stride_token = (int64_t)num_kv_heads * head_dim;
+    out->stride_block = (int64_t)max_seq_len * out->stride_token;
+    return GQA_OK;
+}
+
+int gqa_layout_pool(int32_t num_blocks, int32_t block_tokens, int32_t num_kv_heads,
+                    int32_t head_dim, gqa_kv_layout* out) {
+    if (out == nullptr) return GQA_ERR_NULL;
+    if (num_blocks <= 0 || block_tokens <= 0 || num_kv_heads <= 0 || head_dim <= 0) {
+        return GQA_ERR_SHAPE;
+    }
+    if (block_tokens % GQA_CHUNK_KEYS != 0) return GQA_ERR_SHAPE;
+    std::memset(out, 0, sizeof(*out));
+    out->block_tokens = block_tokens;
+    out->num_blocks = num_blocks;
+    out->stride_token = head_dim;
+    out->stride_head = (int64_t)block_tokens * head_dim;
+    out->stride_block = (int64_t)num_kv_heads * out->stride_head;
+    return GQA_OK;
+}
+
+int gqa_decode_plan(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out) {
+    if (out == nullptr) return GQA_ERR_NULL;
+    int rc = validate_decode(p);
+    if (rc != GQA_OK) return rc;
+    if (sm_count <= 0) {
+        rc = device_sm_count(&sm_count);
+        if (rc != GQA_OK) return rc;
+    }
+    return plan_from_params(p, sm_count, out);
+}
+
+int gqa_decode(const gqa_decode_params* p) {
+    int rc = validate_decode(p);
+    if (rc != GQA_OK) return rc;
+    int32_t sms = 0;
+    rc = device_sm_count(&sms);
+    if (rc != GQA_OK) return rc;
+    gqa_decode_plan_info plan;
+    rc = plan_from_params(p, sms, &plan);
+    if (rc != GQA_OK) return rc;
+    if (plan.needs_combine) {
+        if (p->workspace == nullptr) return GQA_ERR_NULL;
+        if (p->workspace_bytes < plan.workspace_bytes) return GQA_ERR_WORKSPACE;
+        if (!aligned16(p->workspace)) return GQA_ERR_ALIGN;
+    }
+
+    gqa::DecodeArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.q = p->q;
+    a.out = p->out;
+    a.workspace = reinterpret_cast<float*>(p->workspace);
+    a.k_cache = p->k_cache;
+    a.v_cache = p->v_cache;
+    a.seq_lens_dev = p->seq_lens_dev;
+    a.block_table = p->block_table_dev;
+    a.status = p->status_dev;
+    a.stride_block = p->layout.stride_block;
+    a.stride_token = p->layout.stride_token;
+    a.stride_head = p->layout.stride_head;
+    a.batch = p->batch;
+    a.num_q_heads = p->num_q_heads;
+    a.num_kv_heads = p->num_kv_heads;
+    a.group = p->num_q_heads / p->num_kv_heads;
+    a.uniform_len = p->seq_lens_dev == nullptr ? p->seq_lens_host[0] : 0;
+    a.split_chunks = plan.split_chunks;
+    a.blocks_per_seq = p->blocks_per_seq;
+    a.block_tokens = p->layout.block_tokens;
+    a.fixed_block = p->fixed_block;
+    a.scale_log2 = (1.0f / sqrtf((float)kHeadDim)) * 1.44269504088896340736f;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(p->stream);
+
+    cudaError_t e;
+    if (p->dtype == GQA_DTYPE_BF16) {
+        CUtensorMap tk, tv;
+        bool head_first = false;
+        const gqa_kv_layout lay = clean_layout(p->layout);
+        rc = cached_cache_map(p->k_cache, lay, p->num_kv_heads, &head_first, &tk);
+        if (rc != GQA_OK) return rc;
+        rc = cached_cache_map(p->v_cache, lay, p->num_kv_heads, &head_first, &tv);
+        if (rc != GQA_OK) return rc;
+        a.head_before_token = head_first ? 1 : 0;
+        e = gqa::launch_stream_bf16(tk, tv, a, plan.num_ctas, stream);
+    } else {
+        e = gqa::launch_stream_f32(a, plan.num_ctas, stream);
+    }
+    if (e != cudaSuccess) return GQA_ERR_CUDA;
+    if (plan.needs_combine) {
+        e = gqa::launch_combine(a, p->dtype == GQA_DTYPE_BF16, stream);
+        if (e != cudaSuccess) return GQA_ERR_CUDA;
+    }
+    return GQA_OK;
+}
+
+int gqa_qk_norm_rope_append(const gqa_front_params* p) {
+    if (p == nullptr) return GQA_ERR_NULL;
+    if (p->batch <= 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0) return GQA_ERR_SHAPE;
+    if (p->head_dim != kHeadDim) return GQA_ERR_SHAPE;
+    int rc = validate_layout(p->layout, GQA_DTYPE_BF16, p->num_kv_heads);
+    if (rc != GQA_OK) return rc;
+    if (p->q == nullptr || p->q_out == nullptr || p->k_new == nullptr || p->qk_weight == nullptr ||
+        p->k_cache == nullptr) {
+        return GQA_ERR_NULL;
+    }
+    if (p->v_new != nullptr && p->v_cache == nullptr) return GQA_ERR_NULL;
+    if ((p->sin_cache == nullptr) != (p->cos_cache == nullptr)) return GQA_ERR_NULL;
+    if (p->positions_host == nullptr && p->positions_dev == nullptr) return GQA_ERR_NULL;
+    if (p->v_new != nullptr && (!aligned16(p->v_new) || !aligned16(p->v_cache))) {
+        return GQA_ERR_ALIGN;
+    }
+    int64_t capacity;
+    if (p->block_table_dev != nullptr) {
+        if (p->blocks_per_seq <= 0) return GQA_ERR_SHAPE;
+        capacity = (int64_t)p->blocks_per_seq * p->layout.block_tokens;
+    } else {
+        if (p->batch != 1) return GQA_ERR_SHAPE;
+        if (p->fixed_block < 0 || p->fixed_block >= p->layout.num_blocks) return GQA_ERR_RANGE;
+        capacity = p->layout.block_tokens;
+    }
+    int32_t uniform_pos = 0;
+    if (p->positions_host != nullptr) {
+        for (int32_t b = 0; b < p->batch; ++b) {
+            const int32_t pos = p->positions_host[b];
+            if (pos < 0 || pos >= capacity) return GQA_ERR_RANGE;
+            if (p->sin_cache != nullptr && pos >= p->table_len) return GQA_ERR_RANGE;
+            if (p->positions_dev == nullptr && pos != p->positions_host[0]) {
+                return GQA_ERR_UNSUPPORTED;
+            }
+        }
+        uniform_pos = p->positions_host[0];
+    }
+    gqa::FrontArgs f;
+    std::memset(&f, 0, sizeof(f));
+    f.q = p->q;
+    f.q_out = p->q_out;
+    f.k_new = p->k_new;
+    f.v_new = p->v_new;
+    f.qk_weight = p->qk_weight;
+    f.k_cache = p->k_cache;
+    f.v_cache = p->v_cache;
+    f.sin_cache = p->sin_cache;
+    f.cos_cache = p->cos_cache;
+    f.positions_dev = p->positions_dev;
+    f.block_table = p->block_table_dev;
+    f.stride_block = p->layout.stride_block;
+    f.stride_token = p->layout.stride_token;
+    f.stride_head = p->layout.stride_head;
+    f.batch = p->batch;
+    f.num_q_heads = p->num_q_heads;
+    f.num_kv_heads = p->num_kv_heads;
+    f.uniform_pos = uniform_pos;
+    f.blocks_per_seq = p->blocks_per_seq;
+    f.block_tokens = p->layout.block_tokens;
+    f.fixed_block = p->fixed_block;
+    f.eps = p->eps;
+    const cudaError_t e = gqa::launch_front(f, reinterpret_cast<cudaStream_t>(p->stream));
+    return e == cudaSuccess ? GQA_OK : GQA_ERR_CUDA;
+}
+
+int gqa_sin_cos_cache(float* sin_cache, float* cos_cache, int32_t head_dim, int32_t max_seq_len,
+                      void* stream) {
+    if (sin_cache == nullptr || cos_cache == nullptr) return GQA_ERR_NULL;
+    if (head_dim <= 0 || (head_dim & 1) || max_seq_len <= 0) return GQA_ERR_SHAPE;
+    const cudaError_t e = gqa::launch_sin_cos(sin_cache, cos_cache, head_dim, max_seq_len,
+                                              reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? GQA_OK : GQA_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+// How a decode-attention launch is cut into work items, shared by the streaming kernels and
+// the combine kernel so that both sides address the same partial records.
+//
+//   unit  = (sequence b, kv head hk): one pass over that head's cached keys, shared by the
+//           `group` query heads that read it;
+//   chunk = 32 consecutive keys of a unit;
+//   item  = (unit, split): `split_chunks` consecutive chunks of a unit. Item ids are
+//           sequence-major, then kv head, then split, so the partial record of an item sits
+//           at workspace + item * group * (head_dim + 2) floats: O[group][head_dim] scaled
+//           to the item's own running maximum, then m[group], then l[group].
+#pragma once
+
+#include <cstdint>
+
+namespace gqa {
+
+constexpr int kChunkKeys = 32;
+constexpr int kHeadDim = 128;
+constexpr int kMaxRaggedBatch = 1024;
+
+struct DecodeArgs {
+    const void* q;
+    void* out;
+    float* workspace;
+    const void* k_cache;
+    const void* v_cache;
+    const int32_t* seq_lens_dev;  // null: every sequence has `uniform_len` keys
+    const int32_t* block_table;   // null: every chunk reads block `fixed_block`
+    int32_t* status;
+    int64_t stride_block;
+    int64_t stride_token;
+    int64_t stride_head;
+    int32_t batch;
+    int32_t num_q_heads;
+    int32_t num_kv_heads;
+    int32_t group;
+    int32_t uniform_len;
+    int32_t split_chunks;
+    int32_t blocks_per_seq;
+    int32_t block_tokens;
+    int32_t fixed_block;
+    int32_t head_before_token;  // order of the middle tensor-map coordinates (BF16 path)
+    float scale_log2;  // (1 / sqrt(head_dim)) * log2(e)
+};
+
+struct Item {
+    int32_t b;
+    int32_t hk;
+    int32_t split;
+    int32_t nsplits;
+    int32_t len;
+    int32_t chunk_begin;
+    int32_t chunk_end;
+};
+
+__host__ __device__ inline int32_t ceil_div(int32_t a, int32_t b) { return (a + b - 1) / b; }
+
+// Tables for ragged batches, built in shared memory by every CTA: s_len[b] and
+// s_base[b] = items of sequences before b (s_base[batch] = total).
+struct WorkTables {
+    const int32_t* s_len;
+    const int32_t* s_base;
+};
+
+// Must be called by all threads of the CTA; needs 2 * (batch + 1) ints of shared memory.
+__device__ inline WorkTables build_work_tables(const DecodeArgs& a, int32_t* smem_ints) {
+    WorkTables t{nullptr, nullptr};
+    if (a.seq_lens_dev == nullptr) return t;
+    int32_t* s_len = smem_ints;
+    int32_t* s_base = smem_ints + (a.batch + 1);
+    for (int32_t b = threadIdx.x; b < a.batch; b += blockDim.x) {
+        s_len[b] = a.seq_lens_dev[b];
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        // Warp scan over contiguous segments of the batch.
+        const int32_t per = ceil_div(a.batch, 32);
+        const int32_t lo = min(a.batch, (int32_t)threadIdx.x * per);
+        const int32_t hi = min(a.batch, lo + per);
+        int32_t sum = 0;
+        for (int32_t b = lo; b < hi; ++b) {
+            const int32_t chunks = ceil_div(max(s_len[b], 0), kChunkKeys);
+            sum += ceil_div(chunks, a.split_chunks) * a.num_kv_heads;
+        }
+        int32_t incl = sum;
+        for (int32_t d = 1; d < 32; d <<= 1) {
+            const int32_t up = __shfl_up_sync(0xffffffffu, incl, d);
+            if ((int32_t)threadIdx.x >= d) incl += up;
+        }
+        int32_t run = incl - sum;
+        for (int32_t b = lo; b < hi; ++b) {
+            s_base[b] = run;
+            const int32_t chunks = ceil_div(max(s_len[b], 0), kChunkKeys);
+            run += ceil_div(chunks, a.split_chunks) * a.num_kv_heads;
+        }
+        if (threadIdx.x == 31) s_base[a.batch] = incl;
+    }
+    __syncthreads();
+    t.s_len = s_len;
+    t.s_base = s_base;
+    return t;
+}
+
+__device__ inline int32_t total_items(const DecodeArgs& a, const WorkTables& t) {
+    if (t.s_base != nullptr) return t.s_base[a.batch];
+    const int32_t chunks = ceil_div(a.uniform_len, kChunkKeys);
+    return a.batch * a.num_kv_heads * ceil_div(chunks, a.split_chunks);
+}
+
+__device__ inline Item decode_item(const DecodeArgs& a, const WorkTables& t, int32_t item) {
+    Item it;
+    int32_t within;
+    if (t.s_base != nullptr) {
+        int32_t lo = 0, hi = a.batch;  // largest b with s_base[b] <= item
+        while (hi - lo > 1) {
+            const int32_t mid = (lo + hi) >> 1;
+            if (t.s_base[mid] <= item) lo = mid; else hi = mid;
+        }
+        it.b = lo;
+        it.len = t.s_len[lo];
+        within = item - t.s_base[lo];
+    } else {
+        const int32_t chunks = ceil_div(a.uniform_len, kChunkKeys);
+        const int32_t per_seq = a.num_kv_heads * ceil_div(chunks, a.split_chunks);
+        it.b = item / per_seq;
+        it.len = a.uniform_len;
+        within = item - it.b * per_seq;
+    }
+    const int32_t chunks = ceil_div(it.len, kChunkKeys);
+    it.nsplits = ceil_div(chunks, a.split_chunks);
+    it.hk = within / it.nsplits;
+    it.split = within - it.hk * it.nsplits;
+    it.chunk_begin = it.split * a.split_chunks;
+    it.chunk_end = min(chunks, it.chunk_begin + a.split_chunks);
+    return it;
+}
+
+// First item and split count of unit (b, hk), for the combine kernel.
+__device__ inline void unit_items(const DecodeArgs& a, const WorkTables& t, int32_t b, int32_t hk,
+                                  int32_t* first_item, int32_t* nsplits) {
+    int32_t len, base;
+    if (t.s_base != nullptr) {
+        len = t.s_len[b];
+        base = t.s_base[b];
+    } else {
+        len = a.uniform_len;
+        const int32_t chunks = ceil_div(len, kChunkKeys);
+        base = b * a.num_kv_heads * ceil_div(chunks, a.split_chunks);
+    }
+    const int32_t chunks = ceil_div(len, kChunkKeys);
+    *nsplits = ceil_div(chunks, a.split_chunks);
+    *first_item = base + hk * (*nsplits);
+}
+
+}  // namespace gqa

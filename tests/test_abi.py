@@ -1,0 +1,184 @@
+"""Host-side behaviour of the C ABI that needs no GPU: the library loads and exports every
+symbol the header declares, argument validation returns the documented codes, the split
+planner, the KV block pool and the head-parallel partition."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def gqa(built_lib):
+    import llminfer_b200 as pkg
+    return pkg
+
+
+def test_library_exports_every_declared_symbol(gqa):
+    header = (ROOT / "include" / "gqa_b200.h").read_text()
+    declared = set(re.findall(r"\b(gqa_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 25
+    handle = gqa.lib()
+    for name in sorted(declared):
+        assert hasattr(handle, name), f"{name} is declared in the header but not exported"
+    assert declared == set(gqa.binding.exported_symbols())
+    assert handle.gqa_abi_version() == 1
+    assert gqa.status_string(0) == "ok"
+    assert "workspace" in gqa.status_string(-6)
+
+
+def test_missing_library_fails_loudly(monkeypatch, gqa, tmp_path):
+    from llminfer_b200 import binding
+    monkeypatch.setattr(binding, "_lib", None)
+    monkeypatch.setattr(binding, "_LIB_PATH", tmp_path / "libgqa_b200.so")
+    with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
+        binding.lib()
+
+
+def test_layouts(gqa):
+    ref = gqa.layout_reference(36, 4096, 8)
+    assert (ref.block_tokens, ref.num_blocks) == (4096, 36)
+    assert (ref.stride_head, ref.stride_token, ref.stride_block) == (128, 1024, 4096 * 1024)
+    pool = gqa.layout_pool(100, 256, 8)
+    assert (pool.stride_token, pool.stride_head, pool.stride_block) == (128, 256 * 128, 8 * 256 * 128)
+    with pytest.raises(gqa.GqaError) as e:
+        gqa.layout_pool(100, 100, 8)  # not a multiple of the 32-key chunk
+    assert e.value.status == -3
+
+
+def plan(gqa, **kw):
+    base = dict(dtype=2, batch=1, num_q_heads=32, num_kv_heads=8,
+                layout=gqa.layout_reference(1, 131072, 8), seq_lens=[1024])
+    base.update(kw)
+    return gqa.decode_plan(**base)
+
+
+def test_validation_codes(gqa):
+    codes = {}
+    for name, kw in {
+        "dtype": dict(dtype=3),
+        "head_dim": dict(head_dim=64),
+        "group_not_integer": dict(num_q_heads=30),
+        "group_too_wide": dict(num_q_heads=128),
+        "len_zero": dict(seq_lens=[0]),
+        "len_past_cache": dict(seq_lens=[131073]),
+        "block_out_of_range": dict(fixed_block=1),
+        "batch_needs_table": dict(batch=2, seq_lens=[5, 5]),
+        "ragged_needs_device_lens": dict(batch=2, seq_lens=[5, 6], paged=True, blocks_per_seq=1),
+        "negative_split": dict(split_keys=-1),
+    }.items():
+        with pytest.raises(gqa.GqaError) as e:
+            plan(gqa, **kw)
+        codes[name] = e.value.status
+    assert codes == {"dtype": -2, "head_dim": -3, "group_not_integer": -3, "group_too_wide": -8,
+                     "len_zero": -5, "len_past_cache": -5, "block_out_of_range": -5,
+                     "batch_needs_table": -3, "ragged_needs_device_lens": -8,
+                     "negative_split": -5}
+    bad = gqa.KvLayout(4096, 1, 4096 * 1024, 1028, 128)  # token stride not 16-byte aligned
+    with pytest.raises(gqa.GqaError) as e:
+        plan(gqa, layout=bad)
+    assert e.value.status == -4
+
+
+def test_compute_entry_points_reject_bad_arguments_before_touching_the_device(gqa):
+    handle = gqa.lib()
+    assert handle.gqa_decode(None) == -1
+    assert handle.gqa_qk_norm_rope_append(None) == -1
+    assert handle.gqa_sin_cos_cache(None, None, 128, 16, None) == -1
+    out = C.c_void_p()
+    assert handle.gqa_session_create(1, 1, 32, 8, 128, 64, C.byref(out)) == -2  # FP32 session
+    assert handle.gqa_session_create(2, 1, 32, 8, 64, 64, C.byref(out)) == -3
+
+
+def test_planner_short_context_needs_no_second_launch(gqa):
+    p = plan(gqa, seq_lens=[96])
+    assert p["needs_combine"] == 0 and p["workspace_bytes"] == 0
+    assert p["num_items"] == 8 and p["num_ctas"] == 8 and p["max_splits"] == 1
+
+
+def test_planner_fills_the_gpu_at_long_context(gqa):
+    for hq, batch, length in ((32, 1, 32768), (64, 4, 131072), (32, 1, 1024)):
+        layout = gqa.layout_pool(batch * (length // 256), 256, 8)
+        p = gqa.decode_plan(dtype=2, batch=batch, num_q_heads=hq, num_kv_heads=8, layout=layout,
+                            seq_lens=[length] * batch, paged=True, blocks_per_seq=length // 256,
+                            device_lens=True)
+        chunks = length // 32
+        assert p["needs_combine"] == 1
+        assert p["num_ctas"] >= 128 or p["num_items"] < 148
+        rounds = -(-p["num_items"] // 148)
+        # No CTA works on more than ~6% above its fair share of the chunks.
+        per_cta = rounds * p["split_chunks"]
+        fair = batch * 8 * chunks / 148
+        assert per_cta <= max(1.10 * fair + 4, 8), (length, p)
+        assert p["workspace_bytes"] == p["num_items"] * (hq // 8) * 130 * 4
+
+
+def test_planner_respects_overrides_and_workspace(gqa):
+    p = plan(gqa, seq_lens=[4096], split_keys=100)
+    assert p["split_chunks"] == 4 and p["max_splits"] == 32 and p["num_items"] == 256
+    p = plan(gqa, seq_lens=[4096], max_ctas=16)
+    assert p["num_ctas"] <= 16
+    small = 8 * 4 * 130 * 4 * 3  # room for three splits per unit
+    p = plan(gqa, seq_lens=[32768], workspace_bytes=small)
+    assert p["workspace_bytes"] <= small and p["max_splits"] <= 3
+    with pytest.raises(gqa.GqaError) as e:
+        plan(gqa, seq_lens=[32768], workspace_bytes=small, split_keys=64)
+    assert e.value.status == -6
+
+
+def test_planner_device_lengths_size_the_scratch_for_full_sequences(gqa):
+    layout = gqa.layout_pool(16 * 32, 256, 8)
+    p = gqa.decode_plan(dtype=2, batch=16, num_q_heads=32, num_kv_heads=8, layout=layout,
+                        seq_lens=None, paged=True, blocks_per_seq=32, device_lens=True,
+                        plan_len_hint=4096)
+    full_items = 16 * 8 * -(-(32 * 256 // 32) // p["split_chunks"])
+    assert p["num_items"] == full_items
+    assert p["workspace_bytes"] == full_items * 4 * 130 * 4
+
+
+def test_kv_pool_bookkeeping(gqa):
+    pool = gqa.KvPool(num_blocks=10, block_tokens=256, num_kv_heads=8, max_seqs=4,
+                      max_blocks_per_seq=4)
+    assert pool.bytes == 10 * 8 * 256 * 128 * 2
+    assert pool.layout() == gqa.layout_pool(10, 256, 8)
+    pool.reserve(0, 1)
+    pool.reserve(1, 600)
+    pool.reserve(0, 257)
+    table = pool.table()
+    assert table[0].tolist() == [0, 4, -1, -1] and table[1].tolist() == [1, 2, 3, -1]
+    assert pool.free_blocks() == 5 and pool.seq_blocks(1) == 3
+    pool.reserve(1, 100)  # shrinking requests keep what is held
+    assert pool.seq_blocks(1) == 3
+    with pytest.raises(gqa.GqaError) as e:
+        pool.reserve(2, 5 * 256)  # more blocks than a sequence may hold
+    assert e.value.status == -5
+    pool.reserve(2, 4 * 256)
+    with pytest.raises(gqa.GqaError) as e:
+        pool.reserve(3, 2 * 256)  # only one block left: nothing is taken
+    assert e.value.status == -10 and pool.free_blocks() == 1 and pool.seq_blocks(3) == 0
+    pool.release(1)
+    assert pool.free_blocks() == 4 and pool.table()[1].tolist() == [-1] * 4
+    pool.reserve(3, 2 * 256)
+    used = [b for row in pool.table().tolist() for b in row if b >= 0]
+    assert len(used) == len(set(used)) == 8
+    pool.close()
+    assert gqa.lib().gqa_kv_pool_bytes(10, 100, 8, 128, 2) == 0
+
+
+def test_shard_plan(gqa):
+    for n in (1, 2, 4, 8):
+        seen = []
+        for r in range(n):
+            s = gqa.shard_plan(64, 8, n, r)
+            assert s["num_local_kv_heads"] == 8 // n and s["num_local_q_heads"] == 64 // n
+            assert s["first_q_head"] == s["first_kv_head"] * 8
+            seen += list(range(s["first_kv_head"], s["first_kv_head"] + s["num_local_kv_heads"]))
+        assert seen == list(range(8))
+    with pytest.raises(gqa.GqaError) as e:
+        gqa.shard_plan(64, 8, 3, 0)
+    assert e.value.status == -3
+    with pytest.raises(gqa.GqaError) as e:
+        gqa.shard_plan(64, 8, 4, 4)
+    assert e.value.status == -5
