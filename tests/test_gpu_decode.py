@@ -36,7 +36,8 @@ def run_reference_layout(gqa, q_bits, k_bits, v_bits, *, hkv, layer_id, length, 
     q = H.bf16_tensor(q_bits).reshape(1, hq, H.D)
     k, v = H.bf16_tensor(k_bits), H.bf16_tensor(v_bits)
     out = torch.full((1, hq, H.D), float("nan"), dtype=torch.bfloat16, device="cuda:0")
-    ws = torch.empty(hq * 4 * max(max_seq_len, 64), dtype=torch.float32, device="cuda:0")
+    # One partial record per 32 keys per query head is the most any split can need.
+    ws = torch.empty(hq * 130 * (max_seq_len // 32 + 1), dtype=torch.float32, device="cuda:0")
     status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
     gqa.decode(q, k, v, out, num_kv_heads=hkv, layout=layout, seq_lens=[length],
                fixed_block=layer_id, workspace=ws, split_keys=split_keys, max_ctas=max_ctas,
