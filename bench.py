@@ -35,19 +35,30 @@ sys.path.insert(0, str(ROOT))
 
 HEAD_DIM = 128
 BLOCK_TOKENS = 256
-WORKLOADS = {
-    # name: query heads, kv heads, batch, cached length
-    "qwen3-32b-bf16-b4-ctx131072": (64, 8, 4, 131072),
-    "qwen3-4b-bf16-b1-ctx32768": (32, 8, 1, 32768),
-    "qwen3-4b-bf16-b1-ctx1024": (32, 8, 1, 1024),
-}
-DEFAULT_WORKLOAD = "qwen3-32b-bf16-b4-ctx131072"
 MIN_RESIDENT_BYTES = 1 << 30  # distinct KV bytes cycled per GPU, several times the 126 MB L2
 
 
-def algorithmic_bytes(hq: int, hkv: int, lens) -> int:
-    """K and V read once per KV head, q read, out written (BF16)."""
-    return sum(2 * l * hkv * HEAD_DIM * 2 for l in lens) + 2 * len(lens) * hq * HEAD_DIM * 2
+def _ragged_lengths(batch: int = 16, lo: int = 256, hi: int = 8192, seed: int = 20260614 + 4):
+    import random
+    rnd = random.Random(seed)
+    return [rnd.randint(lo, hi) for _ in range(batch)]
+
+
+# name: (query heads, kv heads, per-sequence cached lengths, cache layout, dtype)
+WORKLOADS = {
+    "qwen3-32b-bf16-b4-ctx131072": (64, 8, [131072] * 4, "pool", "bf16"),
+    "qwen3-32b-bf16-b1-ctx131072": (64, 8, [131072], "pool", "bf16"),
+    "qwen3-8b-bf16-b16-ragged256-8192": (32, 8, _ragged_lengths(), "pool", "bf16"),
+    "qwen3-4b-bf16-b1-ctx32768": (32, 8, [32768], "reference", "bf16"),
+    "qwen3-4b-bf16-b1-ctx1024": (32, 8, [1024], "reference", "bf16"),
+    "qwen3-0.6b-f32-b1-ctx512": (16, 8, [512], "reference", "f32"),
+}
+DEFAULT_WORKLOAD = "qwen3-32b-bf16-b4-ctx131072"
+
+
+def algorithmic_bytes(hq: int, hkv: int, lens, elem: int = 2) -> int:
+    """K and V read once per KV head, q read, out written."""
+    return sum(2 * l * hkv * HEAD_DIM * elem for l in lens) + 2 * len(lens) * hq * HEAD_DIM * elem
 
 
 class ClockSampler:
@@ -118,9 +129,11 @@ def measured_peak_gbs() -> tuple[float, str]:
 # ---------------------------------------------------------------------------------------------
 # CPU arm: the oracle port of the reference's CPU attention on a bounded sample
 # ---------------------------------------------------------------------------------------------
-def cpu_sample_us_per_layer(hq: int, hkv: int, batch: int, length: int, reps: int,
-                            warmup: int) -> dict:
-    """Times one sequence (all heads) on all host threads and scales by the batch size."""
+def cpu_sample_us_per_layer(hq: int, hkv: int, lens, reps: int, warmup: int) -> dict:
+    """Times the longest sequence (all heads) on all host threads and scales by total keys."""
+    batch = len(lens)
+    length = max(lens)
+    scale = sum(lens) / length
     import numpy as np
     from oracle import oracle
 
@@ -152,9 +165,10 @@ def cpu_sample_us_per_layer(hq: int, hkv: int, batch: int, length: int, reps: in
         if i >= warmup:
             times.append(time.perf_counter() - t0)
     per_seq = sum(times) / len(times)
-    return {"value": per_seq * batch * 1e6, "unit": "us/layer", "cores": threads, "kind": "port",
+    return {"value": per_seq * scale * 1e6, "unit": "us/layer", "cores": threads, "kind": "port",
             "sample": f"1 of {batch} sequences ({hq} q heads, {hkv} kv heads, {sample_len} keys, "
-                      f"FP32 math on BF16 values), all {threads} host threads, scaled x{batch}",
+                      f"FP32 math on BF16-rounded values), all {threads} host threads, scaled "
+                      f"x{scale:.3g} by key count",
             "seconds_per_sample": per_seq}
 
 
@@ -162,9 +176,10 @@ def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    hq, hkv, batch, length = WORKLOADS[args.workload]
+    hq, hkv, lens, _, _ = WORKLOADS[args.workload]
+    batch, length = len(lens), max(lens)
     steps = max(1, min(args.steps, 5))
-    res = cpu_sample_us_per_layer(hq, hkv, batch, length, reps=steps, warmup=min(args.warmup, 1))
+    res = cpu_sample_us_per_layer(hq, hkv, lens, reps=steps, warmup=min(args.warmup, 1))
     line = {
         "impl": "reference", "metric": "gqa_decode_attn_us_per_layer", "value": res["value"],
         "unit": "us/layer", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
@@ -202,61 +217,93 @@ def run_ours(args) -> None:
         dist.broadcast_object_list(ident, src=0)
         comm = gqa.ShardComm(ident[0], world, rank)
 
-    hq_total, hkv_total, batch, length = WORKLOADS[args.workload]
+    hq_total, hkv_total, lens, layout_kind, dtype_name = WORKLOADS[args.workload]
+    batch = len(lens)
     shard = gqa.shard_plan(hq_total, hkv_total, world, rank)
     hq, hkv = shard["num_local_q_heads"], shard["num_local_kv_heads"]
-    pos = length - 1
-    lens = [length] * batch
-    blocks_per_seq = length // BLOCK_TOKENS
-    blocks_per_slot = batch * blocks_per_seq
-    slot_bytes = 2 * blocks_per_slot * hkv * BLOCK_TOKENS * HEAD_DIM * 2
-    slots = max(1, -(-MIN_RESIDENT_BYTES // slot_bytes))
-    num_blocks = slots * blocks_per_slot
-    layout = gqa.layout_pool(num_blocks, BLOCK_TOKENS, hkv)
-
+    tdtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
+    elem = 2 if dtype_name == "bf16" else 4
     gen = torch.Generator(device=dev)
     gen.manual_seed(20260614 + rank)
-    pool_elems = num_blocks * hkv * BLOCK_TOKENS * HEAD_DIM
-    k_pool = torch.empty(pool_elems, dtype=torch.bfloat16, device=dev)
-    v_pool = torch.empty(pool_elems, dtype=torch.bfloat16, device=dev)
-    piece = 1 << 26
-    for pool in (k_pool, v_pool):
-        for start in range(0, pool_elems, piece):
-            n = min(piece, pool_elems - start)
-            pool[start:start + n] = torch.randn(n, device=dev, generator=gen).to(torch.bfloat16)
-    cpu_gen = torch.Generator().manual_seed(7)
-    tables = []
-    for s in range(slots):
-        perm = torch.randperm(blocks_per_slot, generator=cpu_gen) + s * blocks_per_slot
-        tables.append(perm.to(torch.int32).view(batch, blocks_per_seq).to(dev))
-    q_raw = torch.randn(batch, hq, HEAD_DIM, device=dev, generator=gen).to(torch.bfloat16)
-    k_new = torch.randn(batch, hkv, HEAD_DIM, device=dev, generator=gen).to(torch.bfloat16)
-    v_new = torch.randn(batch, hkv, HEAD_DIM, device=dev, generator=gen).to(torch.bfloat16)
+
+    def randn_fill(t: "torch.Tensor") -> None:
+        flat, piece = t.view(-1), 1 << 26
+        for start in range(0, flat.numel(), piece):
+            n = min(piece, flat.numel() - start)
+            flat[start:start + n] = torch.randn(n, device=dev, generator=gen).to(tdtype)
+
+    positions = [l - 1 for l in lens]  # the new token is the last cached position
+    if layout_kind == "pool":
+        blocks_per_seq = -(-max(lens) // BLOCK_TOKENS)
+        seq_blocks = [-(-l // BLOCK_TOKENS) for l in lens]
+        blocks_per_slot = sum(seq_blocks)
+        slot_bytes = 2 * blocks_per_slot * hkv * BLOCK_TOKENS * HEAD_DIM * elem
+        slots = max(1, -(-MIN_RESIDENT_BYTES // slot_bytes))
+        layout = gqa.layout_pool(slots * blocks_per_slot, BLOCK_TOKENS, hkv)
+        cache_shape = (slots * blocks_per_slot * hkv * BLOCK_TOKENS * HEAD_DIM,)
+        cpu_gen = torch.Generator().manual_seed(7)
+        tables = []
+        for s_ in range(slots):
+            perm = (torch.randperm(blocks_per_slot, generator=cpu_gen) + s_ * blocks_per_slot).tolist()
+            table = torch.full((batch, blocks_per_seq), -1, dtype=torch.int32)
+            for b, nb in enumerate(seq_blocks):
+                table[b, :nb] = torch.tensor([perm.pop() for _ in range(nb)], dtype=torch.int32)
+            tables.append(table.to(dev))
+        layout_note = f"paged pool, {BLOCK_TOKENS}-token blocks, shuffled block order"
+    else:
+        assert batch == 1
+        max_seq_len = lens[0]
+        slot_bytes = 2 * max_seq_len * hkv * HEAD_DIM * elem
+        slots = max(1, -(-MIN_RESIDENT_BYTES // slot_bytes))
+        if lens[0] <= 1024:
+            slots = 36  # the Qwen3-4B layer count: 36 independent caches, one per step
+        layout = gqa.layout_reference(slots, max_seq_len, hkv)
+        cache_shape = (slots, max_seq_len, hkv * HEAD_DIM)
+        blocks_per_seq = 0
+        tables = [None] * slots
+        layout_note = "reference cache [layer, max_seq_len, kv_dim], one layer per step"
+    k_pool = torch.empty(cache_shape, dtype=tdtype, device=dev)
+    v_pool = torch.empty(cache_shape, dtype=tdtype, device=dev)
+    randn_fill(k_pool)
+    randn_fill(v_pool)
+    q_raw = torch.randn(batch, hq, HEAD_DIM, device=dev, generator=gen).to(tdtype)
+    k_new = torch.randn(batch, hkv, HEAD_DIM, device=dev, generator=gen).to(tdtype)
+    v_new = torch.randn(batch, hkv, HEAD_DIM, device=dev, generator=gen).to(tdtype)
     weight = (1.0 + 0.05 * torch.randn(2 * HEAD_DIM, device=dev, generator=gen)).to(torch.bfloat16)
     q_rot = torch.empty_like(q_raw)
-    out = torch.empty(batch, hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
-    gathered = torch.empty(world, batch, hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
-    positions_dev = torch.full((batch,), pos, dtype=torch.int32, device=dev)
+    out = torch.empty(batch, hq, HEAD_DIM, dtype=tdtype, device=dev)
+    gathered = torch.empty(world, batch, hq, HEAD_DIM, dtype=tdtype, device=dev)
+    positions_dev = torch.tensor(positions, dtype=torch.int32, device=dev)
     lens_dev = torch.tensor(lens, dtype=torch.int32, device=dev)
     workspace = gqa.binding.workspace_for(batch, hq, hkv, dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    plan = gqa.decode_plan(dtype=2, batch=batch, num_q_heads=hq, num_kv_heads=hkv, layout=layout,
-                           seq_lens=lens, paged=True, blocks_per_seq=blocks_per_seq,
-                           device_lens=True, sm_count=torch.cuda.get_device_properties(dev).multi_processor_count,
+    paged = layout_kind == "pool"
+    has_front = dtype_name == "bf16"  # the front stage is a BF16 kernel
+    plan = gqa.decode_plan(dtype=2 if dtype_name == "bf16" else 1, batch=batch, num_q_heads=hq,
+                           num_kv_heads=hkv, layout=layout, seq_lens=lens, paged=paged,
+                           blocks_per_seq=blocks_per_seq, device_lens=paged,
+                           sm_count=torch.cuda.get_device_properties(dev).multi_processor_count,
                            workspace_bytes=workspace.numel() * 4)
 
     def attention(slot: int) -> None:
-        kw = dict(num_kv_heads=hkv, layout=layout, seq_lens=lens, seq_lens_dev=lens_dev,
-                  block_table=tables[slot], workspace=workspace, status=status)
-        if comm is None:
-            gqa.decode(q_rot, k_pool, v_pool, out, **kw)
+        kw = dict(num_kv_heads=hkv, layout=layout, seq_lens=lens, workspace=workspace,
+                  status=status)
+        if paged:
+            kw.update(seq_lens_dev=lens_dev, block_table=tables[slot])
         else:
-            gqa.decode_sharded(comm, gathered, q_rot, k_pool, v_pool, out, **kw)
+            kw.update(fixed_block=slot)
+        q_in = q_rot if has_front else q_raw
+        if comm is None:
+            gqa.decode(q_in, k_pool, v_pool, out, **kw)
+        else:
+            gqa.decode_sharded(comm, gathered, q_in, k_pool, v_pool, out, **kw)
 
     def step(slot: int) -> None:
-        gqa.qk_norm_rope_append(q_raw, k_new, v_new, weight, k_pool, v_pool, layout=layout,
-                                positions=[pos] * batch, positions_dev=positions_dev,
-                                q_out=q_rot, block_table=tables[slot])
+        if has_front:
+            kw = dict(block_table=tables[slot], positions_dev=positions_dev) if paged else dict(
+                fixed_block=slot)
+            gqa.qk_norm_rope_append(q_raw, k_new, v_new, weight, k_pool, v_pool, layout=layout,
+                                    positions=positions, q_out=q_rot, **kw)
         attention(slot)
 
     def barrier() -> None:
@@ -277,6 +324,14 @@ def run_ours(args) -> None:
         for i in range(warmup):
             fn(i % slots)
         barrier()
+        if args.no_graph:
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for i in range(steps):
+                fn(i % slots)
+            stop.record()
+            barrier()
+            return max_over_ranks(start.elapsed_time(stop))
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             for i in range(steps):
@@ -300,13 +355,24 @@ def run_ours(args) -> None:
     assert int(status.item()) == 0, "a bounded device wait ran out"
 
     # ---- end to end through the host-buffer entry point -----------------------------------
-    session = gqa.Session(batch, hq, hkv, length)
+    if args.attn_only:
+        peak, peak_kind = measured_peak_gbs()
+        achieved = algorithmic_bytes(hq, hkv, lens, elem) / (attn_us * 1e-6) / 1e9
+        if rank == 0:
+            print(json.dumps({"attention_only_us_per_layer": attn_us, "us_per_layer": us_per_layer,
+                              "roofline": {"achieved": achieved, "frac": achieved / peak},
+                              "plan": plan}))
+        return
+    if not has_front:
+        raise SystemExit("the end-to-end leg needs the BF16 front stage; use --attn-only")
+    session = gqa.Session(batch, hq, hkv, max(lens))
     pin = lambda t: t.cpu().pin_memory()
     q_host, k_host, v_host = pin(q_raw), pin(k_new), pin(v_new)
     out_host = torch.empty(world if comm else 1, batch, hq, HEAD_DIM, dtype=torch.bfloat16).pin_memory()
     def e2e_step(i: int) -> None:
-        session.step(q_host, k_host, v_host, weight, k_pool, v_pool, layout, [pos] * batch,
-                     out_host, block_table=tables[i % slots], comm=comm)
+        session.step(q_host, k_host, v_host, weight, k_pool, v_pool, layout, positions,
+                     out_host, block_table=tables[i % slots],
+                     fixed_block=0 if paged else i % slots, comm=comm)
     for i in range(warmup):
         e2e_step(i)
     barrier()
@@ -320,7 +386,7 @@ def run_ours(args) -> None:
     d2h = out_host.numel() * 2
 
     peak, peak_kind = measured_peak_gbs()
-    rank_bytes = algorithmic_bytes(hq, hkv, lens)
+    rank_bytes = algorithmic_bytes(hq, hkv, lens, elem)
     achieved = rank_bytes / (attn_us * 1e-6) / 1e9
     line = {
         "metric": "gqa_decode_attn_us_per_layer", "value": us_per_layer, "unit": "us/layer",
@@ -328,8 +394,8 @@ def run_ours(args) -> None:
         "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": args.workload, "num_q_heads": hq_total, "num_kv_heads": hkv_total,
-                   "head_dim": HEAD_DIM, "batch": batch, "kv_len": length,
-                   "kv_layout": f"paged pool, {BLOCK_TOKENS}-token blocks, shuffled block order",
+                   "head_dim": HEAD_DIM, "batch": batch, "kv_len": max(lens),
+                   "kv_len_total": sum(lens), "kv_layout": layout_note,
                    "parallelism": f"kv-head-parallel x{world}",
                    "l2": f"inputs larger than L2: {slots} cache slot(s) of "
                          f"{slot_bytes / 2**20:.0f} MiB cycled per GPU",
@@ -349,8 +415,7 @@ def run_ours(args) -> None:
         "clocks": clock_info,
     }
     if rank == 0 and world == 1 and not args.no_cpu:
-        hq0, hkv0, b0, l0 = WORKLOADS[args.workload]
-        cpu = cpu_sample_us_per_layer(hq0, hkv0, b0, l0, reps=2, warmup=1)
+        cpu = cpu_sample_us_per_layer(hq_total, hkv_total, lens, reps=2, warmup=1)
         line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if rank == 0:
         print(json.dumps(line))
@@ -367,6 +432,10 @@ def main() -> None:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=tuple(WORKLOADS), default=DEFAULT_WORKLOAD)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="time eager launches instead of a CUDA-graph replay (profiler runs)")
+    ap.add_argument("--attn-only", action="store_true",
+                    help="tuning runs: skip the end-to-end and CPU legs")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

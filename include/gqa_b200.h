@@ -163,8 +163,11 @@ int gqa_decode(const gqa_decode_params* p);
  * row of pos_b; v_new[b] is copied unchanged to the V cache row. BF16 only, FP32 math,
  * one rounding at the end.
  *   q, q_out        [batch, num_q_heads, head_dim]; may alias (the reference works in place).
- *   k_new, v_new    [batch, num_kv_heads, head_dim]. k_new may already be the cache row
- *                   (reference behaviour: the GEMV wrote it there); v_new null = V untouched.
+ *   k_new, v_new    [batch, num_kv_heads, head_dim]. v_new null = V untouched. When k_new
+ *                   and k_cache are the same pointer (and v_new is null) the key already
+ *                   lies in its cache row, as in the reference where the QKV GEMV wrote it
+ *                   there: it is then normalised and rotated in place and the layout is not
+ *                   used for addressing.
  *   sin_cache/cos_cache  FP32 [table_len, head_dim/2] as built by gqa_sin_cos_cache, or
  *                   both null: angles are then computed in the kernel with the same formula.
  *   positions_host  [batch] or null; positions_dev [batch] on the device or null. One of

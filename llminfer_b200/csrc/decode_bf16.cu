@@ -6,10 +6,10 @@
 // every 32 keys. Here a CTA owns work items of one KV head: K and V leave HBM once and serve
 // the whole query group.
 //
-// Data path. Every warp runs its own ring of STAGES stages. A stage holds one chunk of 32
-// keys: K [2][32][64] and V [2][32][64] BF16 (the 128 channels split in two 128-byte halves
-// so that the 128-byte swizzle applies), 16 KiB, filled by four 4-D bulk tensor copies whose
-// completion is counted on the stage's mbarrier. Lane 0 of the warp refills a stage as soon
+// Data path. Every warp runs its own ring of STAGES stages. A stage holds KEYS consecutive
+// keys: K [2][KEYS][64] and V [2][KEYS][64] BF16 (the 128 channels split in two 128-byte
+// halves so that the 128-byte swizzle applies), KEYS * 512 bytes, filled by four 4-D bulk
+// tensor copies whose completion is counted on the stage's mbarrier. Lane 0 of the warp refills a stage as soon
 // as the warp has finished reading it, so each warp keeps STAGES chunks in flight and the
 // CTA keeps WARPS * STAGES * 16 KiB in flight, with no CTA-wide synchronisation inside an
 // item.
@@ -32,9 +32,6 @@ namespace gqa {
 
 namespace {
 
-constexpr int kHalfBytes = kChunkKeys * 128;        // one 64-channel half of a K or V chunk
-constexpr int kTileBytes = 2 * kHalfBytes;          // K or V chunk
-constexpr int kStageBytes = 2 * kTileBytes;         // K + V
 constexpr int kOPitch = 132;                        // floats per head in the merge buffer
 constexpr int kHeadsPad = 8;                        // MMA N
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;   // bounded wait for a staged chunk
@@ -66,10 +63,14 @@ struct Cursor {
 
 }  // namespace
 
-template <int WARPS, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32, 1)
+template <int WARPS, int STAGES, int KEYS, int OCC>
+__global__ void __launch_bounds__(WARPS * 32, OCC)
 gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const DecodeArgs a) {
+    constexpr int kHalfBytes = KEYS * 128;       // one 64-channel half of K or V of a stage
+    constexpr int kTileBytes = 2 * kHalfBytes;   // K or V of a stage
+    constexpr int kStageBytes = 2 * kTileBytes;  // K + V
+    constexpr int MT = KEYS / 16;                // 16-key MMA tiles per stage
     extern __shared__ uint8_t smem_raw[];
     // The swizzle pattern is a function of the shared-memory address: stages sit on 1 KiB.
     uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -90,6 +91,10 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
         prefetch_tensormap(&tmap_k);
         prefetch_tensormap(&tmap_v);
     }
+    // Everything above overlaps the previous kernel of the stream; from here on its results
+    // (the rotated query, the appended K/V rows, the lengths) are read.
+    pdl_wait();
+    pdl_launch_dependents();
     const WorkTables tables = build_work_tables(a, s_tables);
     __syncthreads();
 
@@ -116,8 +121,8 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                 const Item it = decode_item(a, tables, c.item);
                 c.b = it.b;
                 c.hk = it.hk;
-                c.k = it.chunk_begin + warp;
-                c.k_end = it.chunk_end;
+                c.k = it.chunk_begin * kChunkKeys / KEYS + warp;
+                c.k_end = ceil_div(min(it.len, it.chunk_end * kChunkKeys), KEYS);
             }
         }
     };
@@ -126,7 +131,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     auto issue = [&]() {
         if (!prod.valid) return;
         const uint32_t stage = produced % STAGES;
-        const int32_t t0 = prod.k * kChunkKeys;
+        const int32_t t0 = prod.k * KEYS;
         int32_t blk = a.fixed_block;
         int32_t tok = t0;
         if (a.block_table != nullptr) {
@@ -181,8 +186,8 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 if (n < group) {
-                    qf[ks][0] = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16));
-                    qf[ks][1] = __ldg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8));
+                    qf[ks][0] = __ldcg(reinterpret_cast<const uint32_t*>(qrow + ks * 16));
+                    qf[ks][1] = __ldcg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8));
                 } else {
                     qf[ks][0] = 0u;
                     qf[ks][1] = 0u;
@@ -199,7 +204,9 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
         }
 
 #pragma unroll 1
-        for (int32_t k = it.chunk_begin + warp; k < it.chunk_end; k += WARPS) {
+        const int32_t key_end = min(it.len, it.chunk_end * kChunkKeys);
+        const int32_t k_end = ceil_div(key_end, KEYS);
+        for (int32_t k = it.chunk_begin * kChunkKeys / KEYS + warp; k < k_end; k += WARPS) {
             if (dead) break;
             const uint32_t stage = consumed % STAGES;
             const uint32_t parity = (consumed / STAGES) & 1u;
@@ -210,15 +217,15 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
             }
             const uint32_t kbase = ring + stage * kStageBytes;
             const uint32_t vbase = kbase + kTileBytes;
-            const int32_t valid = it.len - k * kChunkKeys;  // keys of this chunk inside the cache
+            const int32_t valid = key_end - k * KEYS;  // keys of this stage inside the item
 
-            if (valid < kChunkKeys) {
+            if (valid < KEYS) {
                 // Rows past the sequence end hold whatever the cache holds there. Zero those
                 // V rows: their probabilities are zero, but 0 * NaN would still poison O.
                 uint8_t* vptr = ring_all + (warp * STAGES + stage) * kStageBytes + kTileBytes;
-                for (int idx = lane; idx < 2 * kChunkKeys * 8; idx += 32) {
-                    const int half = idx / (kChunkKeys * 8);
-                    const int row = (idx / 8) % kChunkKeys;
+                for (int idx = lane; idx < 2 * KEYS * 8; idx += 32) {
+                    const int half = idx / (KEYS * 8);
+                    const int row = (idx / 8) % KEYS;
                     if (row >= valid) {
                         *reinterpret_cast<uint4*>(vptr + half * kHalfBytes + row * 128 +
                                                   (idx & 7) * 16) = make_uint4(0, 0, 0, 0);
@@ -228,17 +235,17 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                 __syncwarp();
             }
 
-            // ---- S^T = K . Q^T for 2 tiles of 16 keys -----------------------------------
-            float s[2][4];
+            // ---- S^T = K . Q^T for MT tiles of 16 keys ----------------------------------
+            float s[MT][4];
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < MT; ++mt) {
                 s[mt][0] = 0.0f; s[mt][1] = 0.0f; s[mt][2] = 0.0f; s[mt][3] = 0.0f;
             }
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 const uint32_t col = ((uint32_t)((ks & 3) * 2) << 4) ^ k_xor;
 #pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
+                for (int mt = 0; mt < MT; ++mt) {
                     uint32_t a0, a1, a2, a3;
                     ldmatrix_x4(kbase + (ks >> 2) * kHalfBytes + mt * 2048 + k_row_off + col,
                                 a0, a1, a2, a3);
@@ -248,20 +255,25 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
 
             // ---- online softmax (exp2 domain) -------------------------------------------
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) s[mt][c] *= a.scale_log2;
             }
-            if (valid < kChunkKeys) {
+            if (valid < KEYS) {
 #pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
+                for (int mt = 0; mt < MT; ++mt) {
                     const int key = mt * 16 + (lane >> 2);
                     if (key >= valid) { s[mt][0] = -INFINITY; s[mt][1] = -INFINITY; }
                     if (key + 8 >= valid) { s[mt][2] = -INFINITY; s[mt][3] = -INFINITY; }
                 }
             }
-            float c0 = fmaxf(fmaxf(s[0][0], s[0][2]), fmaxf(s[1][0], s[1][2]));
-            float c1 = fmaxf(fmaxf(s[0][1], s[0][3]), fmaxf(s[1][1], s[1][3]));
+            float c0 = fmaxf(s[0][0], s[0][2]);
+            float c1 = fmaxf(s[0][1], s[0][3]);
+#pragma unroll
+            for (int mt = 1; mt < MT; ++mt) {
+                c0 = fmaxf(c0, fmaxf(s[mt][0], s[mt][2]));
+                c1 = fmaxf(c1, fmaxf(s[mt][1], s[mt][3]));
+            }
 #pragma unroll
             for (int d = 4; d < 32; d <<= 1) {
                 c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, d));
@@ -274,10 +286,10 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
             m0 = n0;
             m1 = n1;
 
-            uint32_t pb[2][2];
+            uint32_t pb[MT][2];
             float add0 = 0.0f, add1 = 0.0f;
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+            for (int mt = 0; mt < MT; ++mt) {
                 const uint32_t p01 = pack_bf16(ex2_approx(s[mt][0] - n0), ex2_approx(s[mt][1] - n1));
                 const uint32_t p23 = pack_bf16(ex2_approx(s[mt][2] - n0), ex2_approx(s[mt][3] - n1));
                 add0 += bf16_lo_to_f32(p01) + bf16_lo_to_f32(p23);
@@ -300,7 +312,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
             for (int dt = 0; dt < 8; ++dt) {
                 const uint32_t col = ((uint32_t)((dt & 3) * 2) << 4) ^ v_xor;
 #pragma unroll
-                for (int kt = 0; kt < 2; ++kt) {
+                for (int kt = 0; kt < MT; ++kt) {
                     uint32_t a0, a1, a2, a3;
                     ldmatrix_x4_trans(vbase + (dt >> 2) * kHalfBytes + kt * 2048 + v_row_off + col,
                                       a0, a1, a2, a3);
@@ -370,9 +382,9 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     }
 }
 
-size_t stream_bf16_smem_bytes(int warps, int stages, int batch_for_tables) {
+size_t stream_bf16_smem_bytes(int warps, int stages, int keys, int batch_for_tables) {
     size_t bytes = 1024;  // alignment slack
-    bytes += (size_t)warps * stages * kStageBytes;
+    bytes += (size_t)warps * stages * keys * 512;
     bytes += (size_t)warps * kHeadsPad * kOPitch * sizeof(float);
     bytes += 2 * (size_t)warps * kHeadsPad * sizeof(float);
     bytes += (size_t)warps * stages * sizeof(uint64_t);
@@ -380,29 +392,44 @@ size_t stream_bf16_smem_bytes(int warps, int stages, int batch_for_tables) {
     return bytes;
 }
 
-template <int WARPS, int STAGES>
+template <int WARPS, int STAGES, int KEYS, int OCC>
 static cudaError_t launch_variant(const CUtensorMap& tk, const CUtensorMap& tv,
                                   const DecodeArgs& args, int grid, cudaStream_t stream) {
     const int tables = args.seq_lens_dev != nullptr ? args.batch : 0;
-    const size_t smem = stream_bf16_smem_bytes(WARPS, STAGES, tables);
-    auto kernel = gqa_decode_stream_bf16<WARPS, STAGES>;
-    static bool configured = false;  // per process; the attribute is per function
-    static size_t configured_smem = 0;
-    if (!configured || smem > configured_smem) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)stream_bf16_smem_bytes(WARPS, STAGES,
-                                                                         kMaxRaggedBatch));
+    const size_t smem = stream_bf16_smem_bytes(WARPS, STAGES, KEYS, tables);
+    auto kernel = gqa_decode_stream_bf16<WARPS, STAGES, KEYS, OCC>;
+    static size_t configured[64] = {};  // the attribute is per function and per device
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || configured[dev] < smem) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        configured = true;
-        configured_smem = stream_bf16_smem_bytes(WARPS, STAGES, kMaxRaggedBatch);
+        if (dev >= 0 && dev < 64) configured[dev] = smem;
     }
-    kernel<<<grid, WARPS * 32, smem, stream>>>(tk, tv, args);
-    return cudaGetLastError();
+    return launch_pdl(kernel, dim3(grid), dim3(WARPS * 32), smem, stream, tk, tv, args);
 }
 
-cudaError_t launch_stream_bf16(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeArgs& args,
-                               int grid, cudaStream_t stream) {
-    return launch_variant<kStreamWarps, kStreamStages>(tk, tv, args, grid, stream);
+cudaError_t launch_stream_bf16(const StreamShape& shape, const CUtensorMap& tk,
+                               const CUtensorMap& tv, const DecodeArgs& args, int grid,
+                               cudaStream_t stream) {
+#define GQA_VARIANT(W, S, K, O)                                                     \
+    if (shape.warps == W && shape.stages == S && shape.keys == K && shape.ctas_per_sm == O) { \
+        return launch_variant<W, S, K, O>(tk, tv, args, grid, stream);               \
+    }
+    GQA_VARIANT(4, 1, 64, 1)
+    GQA_VARIANT(4, 2, 32, 1)
+    GQA_VARIANT(4, 3, 32, 1)
+    GQA_VARIANT(5, 1, 64, 1)
+    GQA_VARIANT(3, 2, 64, 1)
+    GQA_VARIANT(8, 1, 32, 1)
+    GQA_VARIANT(4, 1, 32, 2)
+    GQA_VARIANT(2, 1, 64, 2)
+    GQA_VARIANT(2, 2, 32, 2)
+    GQA_VARIANT(4, 1, 16, 3)
+    GQA_VARIANT(2, 1, 32, 3)
+#undef GQA_VARIANT
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace gqa

@@ -58,6 +58,8 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_launch_dependents();
     const WorkTables tables = build_work_tables(a, s_tables);
     const int32_t n_items = total_items(a, tables);
     const int32_t group = a.group;
@@ -72,7 +74,7 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
         for (int n = 0; n < G; ++n) {
             q[n] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (n < group) {
-                q[n] = __ldg(reinterpret_cast<const float4*>(
+                q[n] = __ldcg(reinterpret_cast<const float4*>(
                                  reinterpret_cast<const float*>(a.q) +
                                  ((int64_t)it.b * a.num_q_heads + (int64_t)it.hk * group + n) *
                                      kHeadDim) + lane);
@@ -179,9 +181,39 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
     }
 }
 
+constexpr int kCombineTile = 256;  // splits merged per pass
+
+// Block-wide reductions over 128 threads in a fixed order (so results are reproducible).
+__device__ __forceinline__ float block_max_128(float v, float* scratch) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    const float r = fmaxf(fmaxf(scratch[0], scratch[1]), fmaxf(scratch[2], scratch[3]));
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ float block_sum_128(float v, float* scratch) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    const float r = (scratch[0] + scratch[1]) + (scratch[2] + scratch[3]);
+    __syncthreads();
+    return r;
+}
+
+// One CTA per (sequence, query head), thread d owns output channel d. Partial records are
+// read with L1-bypassing loads: they were written by the kernel this one overlaps with. The m and l of up to
+// kCombineTile splits are fetched in parallel and turned into weights in shared memory, then
+// the O rows are accumulated with independent loads; longer split lists are folded tile by
+// tile with a running (M, L).
 template <bool BF16_OUT>
 __global__ void __launch_bounds__(kHeadDim) gqa_decode_combine(const DecodeArgs a) {
     extern __shared__ int32_t s_tables[];
+    __shared__ float s_w[kCombineTile];
+    __shared__ float s_scratch[4];
+    pdl_wait();
+    pdl_launch_dependents();
     const WorkTables tables = build_work_tables(a, s_tables);
     const int32_t b = blockIdx.x / a.num_q_heads;
     const int32_t h = blockIdx.x - b * a.num_q_heads;
@@ -195,23 +227,61 @@ __global__ void __launch_bounds__(kHeadDim) gqa_decode_combine(const DecodeArgs 
     const int d = threadIdx.x;
     const int64_t rec_floats = (int64_t)group * (kHeadDim + 2);
     const float* rec0 = a.workspace + (int64_t)first * rec_floats;
-    float mx = -INFINITY;
-    for (int32_t s = 0; s < nsplits; ++s) {
-        mx = fmaxf(mx, rec0[s * rec_floats + group * kHeadDim + n]);
-    }
-    float acc = 0.f, lsum = 0.f;
-    for (int32_t s = 0; s < nsplits; ++s) {
-        const float* rec = rec0 + s * rec_floats;
-        const float ms = rec[group * kHeadDim + n];
-        const float f = BF16_OUT ? ex2_approx(ms - mx) : exp2f(ms - mx);
-        acc += rec[n * kHeadDim + d] * f;
-        lsum += rec[group * kHeadDim + group + n] * f;
+    const float* m_base = rec0 + group * kHeadDim + n;
+    const float* l_base = m_base + group;
+    const float* o_base = rec0 + n * kHeadDim + d;
+
+    float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
+    for (int32_t base = 0; base < nsplits; base += kCombineTile) {
+        const int32_t cnt = min(kCombineTile, nsplits - base);
+        float mv[kCombineTile / kHeadDim], lv[kCombineTile / kHeadDim];
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < kCombineTile / kHeadDim; ++j) {
+            const int32_t s = d + j * kHeadDim;
+            mv[j] = -INFINITY;
+            lv[j] = 0.f;
+            if (s < cnt) {
+                mv[j] = __ldcg(m_base + (int64_t)(base + s) * rec_floats);
+                lv[j] = __ldcg(l_base + (int64_t)(base + s) * rec_floats);
+            }
+            tmax = fmaxf(tmax, mv[j]);
+        }
+        tmax = block_max_128(tmax, s_scratch);
+        const float m_new = fmaxf(m_run, tmax);
+        const float rescale = BF16_OUT ? ex2_approx(m_run - m_new) : exp2f(m_run - m_new);
+        float lpart = 0.f;
+#pragma unroll
+        for (int j = 0; j < kCombineTile / kHeadDim; ++j) {
+            const int32_t s = d + j * kHeadDim;
+            const float w = BF16_OUT ? ex2_approx(mv[j] - m_new) : exp2f(mv[j] - m_new);
+            if (s < cnt) s_w[s] = w;
+            lpart += lv[j] * w;
+        }
+        const float ltile = block_sum_128(lpart, s_scratch);  // also publishes s_w
+        float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const float* o_tile = o_base + (int64_t)base * rec_floats;
+        int32_t s = 0;
+        for (; s + 8 <= cnt; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __ldcg(o_tile + (int64_t)(s + j) * rec_floats);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) part[j] += v[j] * s_w[s + j];
+        }
+        for (; s < cnt; ++s) part[0] += __ldcg(o_tile + (int64_t)s * rec_floats) * s_w[s];
+        const float tile_acc = ((part[0] + part[1]) + (part[2] + part[3])) +
+                               ((part[4] + part[5]) + (part[6] + part[7]));
+        acc = acc * rescale + tile_acc;
+        l_run = l_run * rescale + ltile;
+        m_run = m_new;
+        __syncthreads();  // s_w is rewritten by the next tile
     }
     const int64_t o_idx = ((int64_t)b * a.num_q_heads + h) * kHeadDim + d;
     if (BF16_OUT) {
-        reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(acc / lsum);
+        reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(acc / l_run);
     } else {
-        reinterpret_cast<float*>(a.out)[o_idx] = acc / lsum;
+        reinterpret_cast<float*>(a.out)[o_idx] = acc / l_run;
     }
 }
 
@@ -219,13 +289,11 @@ cudaError_t launch_stream_f32(const DecodeArgs& args, int grid, cudaStream_t str
     const size_t smem =
         args.seq_lens_dev != nullptr ? 2 * ((size_t)args.batch + 1) * sizeof(int32_t) : 0;
     if (args.group <= 2) {
-        gqa_decode_stream_f32<2><<<grid, kF32Threads, smem, stream>>>(args);
+        return launch_pdl(gqa_decode_stream_f32<2>, dim3(grid), dim3(kF32Threads), smem, stream, args);
     } else if (args.group <= 4) {
-        gqa_decode_stream_f32<4><<<grid, kF32Threads, smem, stream>>>(args);
-    } else {
-        gqa_decode_stream_f32<8><<<grid, kF32Threads, smem, stream>>>(args);
+        return launch_pdl(gqa_decode_stream_f32<4>, dim3(grid), dim3(kF32Threads), smem, stream, args);
     }
-    return cudaGetLastError();
+    return launch_pdl(gqa_decode_stream_f32<8>, dim3(grid), dim3(kF32Threads), smem, stream, args);
 }
 
 cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t stream) {
@@ -233,11 +301,9 @@ cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t s
         args.seq_lens_dev != nullptr ? 2 * ((size_t)args.batch + 1) * sizeof(int32_t) : 0;
     const int grid = args.batch * args.num_q_heads;
     if (bf16_out) {
-        gqa_decode_combine<true><<<grid, kHeadDim, smem, stream>>>(args);
-    } else {
-        gqa_decode_combine<false><<<grid, kHeadDim, smem, stream>>>(args);
+        return launch_pdl(gqa_decode_combine<true>, dim3(grid), dim3(kHeadDim), smem, stream, args);
     }
-    return cudaGetLastError();
+    return launch_pdl(gqa_decode_combine<false>, dim3(grid), dim3(kHeadDim), smem, stream, args);
 }
 
 }  // namespace gqa

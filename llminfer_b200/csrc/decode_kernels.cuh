@@ -10,15 +10,23 @@
 
 namespace gqa {
 
-// Shape of the BF16 streaming kernel: warps per CTA (each with its own staging ring) and
-// stages per ring. 4 x 3 x 16 KiB = 192 KiB of K/V in flight per SM.
-constexpr int kStreamWarps = 4;
-constexpr int kStreamStages = 3;
+// Shape of the BF16 streaming kernel: warps per CTA (each with its own staging ring), stages
+// per ring, keys per stage and CTAs resident per SM. Each CTA keeps
+// warps * stages * keys * 512 bytes of K/V in flight.
+struct StreamShape {
+    int warps;
+    int stages;
+    int keys;
+    int ctas_per_sm;
+};
+constexpr StreamShape kDefaultStreamShape = {4, 1, 64, 1};
 
-size_t stream_bf16_smem_bytes(int warps, int stages, int batch_for_tables);
+size_t stream_bf16_smem_bytes(int warps, int stages, int keys, int batch_for_tables);
 
-cudaError_t launch_stream_bf16(const CUtensorMap& tmap_k, const CUtensorMap& tmap_v,
-                               const DecodeArgs& args, int grid, cudaStream_t stream);
+// The tensor maps must have been encoded with a box of `shape.keys` rows.
+cudaError_t launch_stream_bf16(const StreamShape& shape, const CUtensorMap& tmap_k,
+                               const CUtensorMap& tmap_v, const DecodeArgs& args, int grid,
+                               cudaStream_t stream);
 
 cudaError_t launch_stream_f32(const DecodeArgs& args, int grid, cudaStream_t stream);
 
@@ -47,10 +55,31 @@ struct FrontArgs {
     int32_t blocks_per_seq;
     int32_t block_tokens;
     int32_t fixed_block;
+    int32_t k_in_place;  // k_new already is the cache row: rotate it where it lies
     float eps;
 };
 
 cudaError_t launch_front(const FrontArgs& args, cudaStream_t stream);
+
+// Launches `kernel` so that it may start while the preceding kernel of the stream is still
+// running (programmatic dependent launch). Such a kernel calls pdl_wait() before it touches
+// anything an earlier kernel wrote, and everything before that call overlaps the
+// predecessor's tail and the launch latency.
+template <typename... KernelArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                       cudaStream_t stream, Args&&... args) {
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...);
+}
 
 cudaError_t launch_sin_cos(float* sin_cache, float* cos_cache, int32_t head_dim,
                            int32_t max_seq_len, cudaStream_t stream);

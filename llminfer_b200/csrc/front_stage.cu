@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 
 #include "decode_kernels.cuh"
+#include "ptx.cuh"
 
 namespace gqa {
 
@@ -39,6 +40,8 @@ __global__ void __launch_bounds__(kFrontWarps * 32) qk_norm_rope_append_kernel(c
     const int b = blockIdx.y;
     const int row = blockIdx.x * kFrontWarps + warp;
     const int n_rows = f.num_q_heads + (f.v_new != nullptr ? 2 : 1) * f.num_kv_heads;
+    pdl_wait();
+    pdl_launch_dependents();
     if (row >= n_rows) return;
 
     const int32_t pos = f.positions_dev != nullptr ? f.positions_dev[b] : f.uniform_pos;
@@ -80,7 +83,8 @@ __global__ void __launch_bounds__(kFrontWarps * 32) qk_norm_rope_append_kernel(c
         const int hk = row - f.num_q_heads;
         in = reinterpret_cast<const __nv_bfloat16*>(f.k_new) +
              ((int64_t)b * f.num_kv_heads + hk) * kHeadDim;
-        out = reinterpret_cast<__nv_bfloat16*>(f.k_cache) + cache_off(hk);
+        out = f.k_in_place ? const_cast<__nv_bfloat16*>(in)
+                           : reinterpret_cast<__nv_bfloat16*>(f.k_cache) + cache_off(hk);
         wei += kHeadDim;
     }
 
@@ -134,8 +138,7 @@ __global__ void sin_cos_table_kernel(float* __restrict__ sin_cache, float* __res
 cudaError_t launch_front(const FrontArgs& args, cudaStream_t stream) {
     const int n_rows = args.num_q_heads + (args.v_new != nullptr ? 2 : 1) * args.num_kv_heads;
     dim3 grid((n_rows + kFrontWarps - 1) / kFrontWarps, args.batch);
-    qk_norm_rope_append_kernel<<<grid, kFrontWarps * 32, 0, stream>>>(args);
-    return cudaGetLastError();
+    return launch_pdl(qk_norm_rope_append_kernel, grid, dim3(kFrontWarps * 32), 0, stream, args);
 }
 
 cudaError_t launch_sin_cos(float* sin_cache, float* cos_cache, int32_t head_dim,

@@ -4,6 +4,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -102,6 +103,23 @@ int device_sm_count(int32_t* out) {
     return GQA_OK;
 }
 
+// Kernel shape; GQA_STREAM_SHAPE="warps,stages,keys[,ctas_per_sm]" overrides it for tuning runs.
+gqa::StreamShape stream_shape() {
+    static gqa::StreamShape shape = [] {
+        gqa::StreamShape s = gqa::kDefaultStreamShape;
+        const char* env = std::getenv("GQA_STREAM_SHAPE");
+        int w = 0, st = 0, k = 0, occ = 1;
+        if (env != nullptr && std::sscanf(env, "%d,%d,%d,%d", &w, &st, &k, &occ) >= 3) {
+            s.warps = w;
+            s.stages = st;
+            s.keys = k;
+            s.ctas_per_sm = occ;
+        }
+        return s;
+    }();
+    return shape;
+}
+
 // ---- split planning ------------------------------------------------------------------------
 // Cost of a candidate, in "steps": one step is every warp of a CTA consuming one chunk.
 // A CTA runs its items back to back (its copies run ahead across items), each item ends with
@@ -120,6 +138,7 @@ struct PlanInput {
     int32_t max_ctas;
     int32_t split_keys;
     size_t workspace_bytes;  // 0 = unconstrained
+    int32_t chunk_align;     // splits start on multiples of this many chunks
 };
 
 int64_t items_for(const PlanInput& in, int32_t q, int32_t* max_splits) {
@@ -153,6 +172,7 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
     const size_t rec = record_bytes(in.group);
 
     auto finish = [&](int32_t q) -> int {
+        q = ceil_div(q, in.chunk_align) * in.chunk_align;
         int32_t ms = 0;
         const int64_t items = items_for(in, q, &ms);
         if (items > INT32_MAX) return GQA_ERR_SHAPE;
@@ -211,10 +231,16 @@ int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pl
                                      : p->layout.block_tokens;
         in.uniform_len = p->plan_len_hint > 0 ? p->plan_len_hint : (int32_t)capacity;
     }
-    in.sm_count = sm_count;
+    in.sm_count = sm_count * (p->dtype == GQA_DTYPE_BF16 ? stream_shape().ctas_per_sm : 1);
     in.max_ctas = p->max_ctas;
     in.split_keys = p->split_keys;
     in.workspace_bytes = p->workspace != nullptr ? p->workspace_bytes : 0;
+    const int32_t stage_keys = p->dtype == GQA_DTYPE_BF16 ? stream_shape().keys : kChunkKeys;
+    in.chunk_align = stage_keys > kChunkKeys ? stage_keys / kChunkKeys : 1;
+    if (p->block_table_dev != nullptr && p->blocks_per_seq > 1 &&
+        p->layout.block_tokens % stage_keys != 0) {
+        return GQA_ERR_SHAPE;
+    }
     int rc = make_plan(in, out);
     if (rc != GQA_OK) return rc;
     if (p->seq_lens_host == nullptr) {
@@ -232,7 +258,8 @@ int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pl
         out->max_splits = upper.max_splits;
         out->needs_combine = upper.needs_combine;
         out->workspace_bytes = upper.workspace_bytes;
-        const int32_t g_max = in.max_ctas > 0 && in.max_ctas < sm_count ? in.max_ctas : sm_count;
+        const int32_t g_max =
+            in.max_ctas > 0 && in.max_ctas < in.sm_count ? in.max_ctas : in.sm_count;
         out->num_ctas = upper.num_items < g_max ? upper.num_items : g_max;
     }
     return GQA_OK;
@@ -257,7 +284,7 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 // BF16 cache as a rank-4 tensor (channel, then token/head by ascending stride, then block);
 // the box is one 64-channel half of a 32-key chunk of one head, swizzled in 128-byte rows.
 int encode_cache_map(const void* base, const gqa_kv_layout& l, int32_t num_kv_heads,
-                     bool* head_before_token, CUtensorMap* map) {
+                     int32_t box_keys, bool* head_before_token, CUtensorMap* map) {
     auto fn = encode_fn();
     if (fn == nullptr) return GQA_ERR_CUDA;
     const bool head_first = l.stride_head < l.stride_token;
@@ -274,11 +301,11 @@ int encode_cache_map(const void* base, const gqa_kv_layout& l, int32_t num_kv_he
         box[1] = 1;
         dims[2] = (cuuint64_t)l.block_tokens;
         strides[1] = (cuuint64_t)l.stride_token * 2;
-        box[2] = kChunkKeys;
+        box[2] = (cuuint32_t)box_keys;
     } else {
         dims[1] = (cuuint64_t)l.block_tokens;
         strides[0] = (cuuint64_t)l.stride_token * 2;
-        box[1] = kChunkKeys;
+        box[1] = (cuuint32_t)box_keys;
         dims[2] = (cuuint64_t)num_kv_heads;
         strides[1] = (cuuint64_t)l.stride_head * 2;
         box[2] = 1;
@@ -298,18 +325,19 @@ struct MapCacheEntry {
     const void* base;
     gqa_kv_layout layout;
     int32_t heads;
+    int32_t box_keys;
     bool head_first;
     CUtensorMap map;
 };
 
-int cached_cache_map(const void* base, const gqa_kv_layout& l, int32_t heads, bool* head_first,
-                     CUtensorMap* map) {
+int cached_cache_map(const void* base, const gqa_kv_layout& l, int32_t heads, int32_t box_keys,
+                     bool* head_first, CUtensorMap* map) {
     static std::mutex mu;
     static std::vector<MapCacheEntry> cache;
     static size_t next = 0;
     std::lock_guard<std::mutex> lock(mu);
     for (const auto& e : cache) {
-        if (e.base == base && e.heads == heads &&
+        if (e.base == base && e.heads == heads && e.box_keys == box_keys &&
             std::memcmp(&e.layout, &l, sizeof(gqa_kv_layout)) == 0) {
             *map = e.map;
             *head_first = e.head_first;
@@ -321,7 +349,8 @@ int cached_cache_map(const void* base, const gqa_kv_layout& l, int32_t heads, bo
     e.base = base;
     e.layout = l;
     e.heads = heads;
-    const int rc = encode_cache_map(base, l, heads, &e.head_first, &e.map);
+    e.box_keys = box_keys;
+    const int rc = encode_cache_map(base, l, heads, box_keys, &e.head_first, &e.map);
     if (rc != GQA_OK) return rc;
     if (cache.size() < 32) {
         cache.push_back(e);
@@ -456,12 +485,13 @@ int gqa_decode(const gqa_decode_params* p) {
         CUtensorMap tk, tv;
         bool head_first = false;
         const gqa_kv_layout lay = clean_layout(p->layout);
-        rc = cached_cache_map(p->k_cache, lay, p->num_kv_heads, &head_first, &tk);
+        const gqa::StreamShape shape = stream_shape();
+        rc = cached_cache_map(p->k_cache, lay, p->num_kv_heads, shape.keys, &head_first, &tk);
         if (rc != GQA_OK) return rc;
-        rc = cached_cache_map(p->v_cache, lay, p->num_kv_heads, &head_first, &tv);
+        rc = cached_cache_map(p->v_cache, lay, p->num_kv_heads, shape.keys, &head_first, &tv);
         if (rc != GQA_OK) return rc;
         a.head_before_token = head_first ? 1 : 0;
-        e = gqa::launch_stream_bf16(tk, tv, a, plan.num_ctas, stream);
+        e = gqa::launch_stream_bf16(shape, tk, tv, a, plan.num_ctas, stream);
     } else {
         e = gqa::launch_stream_f32(a, plan.num_ctas, stream);
     }
@@ -489,8 +519,13 @@ int gqa_qk_norm_rope_append(const gqa_front_params* p) {
     if (p->v_new != nullptr && (!aligned16(p->v_new) || !aligned16(p->v_cache))) {
         return GQA_ERR_ALIGN;
     }
+    // The reference hands the kernel the cache row itself (its QKV GEMV wrote the raw key
+    // there); then the key is rotated where it lies and the layout is not used for addressing.
+    const bool k_in_place = p->k_cache == p->k_new && p->v_new == nullptr;
     int64_t capacity;
-    if (p->block_table_dev != nullptr) {
+    if (k_in_place) {
+        capacity = INT32_MAX;
+    } else if (p->block_table_dev != nullptr) {
         if (p->blocks_per_seq <= 0) return GQA_ERR_SHAPE;
         capacity = (int64_t)p->blocks_per_seq * p->layout.block_tokens;
     } else {
@@ -533,6 +568,7 @@ int gqa_qk_norm_rope_append(const gqa_front_params* p) {
     f.blocks_per_seq = p->blocks_per_seq;
     f.block_tokens = p->layout.block_tokens;
     f.fixed_block = p->fixed_block;
+    f.k_in_place = k_in_place ? 1 : 0;
     f.eps = p->eps;
     const cudaError_t e = gqa::launch_front(f, reinterpret_cast<cudaStream_t>(p->stream));
     return e == cudaSuccess ? GQA_OK : GQA_ERR_CUDA;

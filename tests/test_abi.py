@@ -182,3 +182,35 @@ def test_shard_plan(gqa):
     with pytest.raises(gqa.GqaError) as e:
         gqa.shard_plan(64, 8, 4, 4)
     assert e.value.status == -5
+
+
+def test_shim_exports_the_reference_kernel_symbols(built_lib):
+    """The shim library carries kernel::mha_kernel_cu & co. under the reference's mangled names."""
+    import subprocess
+    from llminfer_b200 import build
+    lib = build.build_shim()
+    names = subprocess.run(["nm", "-D", "--defined-only", "-C", str(lib)], capture_output=True,
+                           text=True, check=True).stdout
+    for symbol in ("kernel::mha_kernel_cu(tensor::Tensor const&",
+                   "kernel::fused_qk_norm_rope_kernel_cu(tensor::Tensor const&",
+                   "kernel::sin_cos_cache_precompute_cu(tensor::Tensor const&",
+                   "kernel::get_mha_kernel(base::DeviceType)",
+                   "kernel::get_fused_qk_norm_rope_kernel(base::DeviceType)",
+                   "op::MultiHeadAttention::forward()",
+                   "op::QKNormRoPELaryer::forward()"):
+        assert symbol in names, symbol
+
+
+def test_kernel_shim_compiles_against_the_reference_headers():
+    """Drop-in check: the entry points build with the reference's own tensor headers."""
+    import os
+    import subprocess
+    ref = Path(os.environ.get("LLMINFER_REFERENCE", "/root/reference"))
+    if not (ref / "code" / "include" / "tensor" / "tensor.h").exists():
+        pytest.skip("reference checkout not mounted")
+    cmd = ["g++", "-std=c++17", "-fsyntax-only", "-I", str(ROOT / "oracle" / "ref_build"),
+           "-I", str(ref / "code" / "include"), "-I", "/usr/local/cuda/include",
+           "-I", str(ROOT / "include"), "-I", str(ROOT / "llminfer_b200" / "shim" / "include"),
+           str(ROOT / "llminfer_b200" / "shim" / "src" / "kernel_shim.cpp")]
+    run = subprocess.run(cmd, capture_output=True, text=True)
+    assert run.returncode == 0, run.stderr
