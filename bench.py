@@ -274,6 +274,9 @@ def run_ours(args) -> None:
     out = torch.empty(batch, hq, HEAD_DIM, dtype=tdtype, device=dev)
     gathered = torch.empty(world, batch, hq, HEAD_DIM, dtype=tdtype, device=dev)
     positions_dev = torch.tensor(positions, dtype=torch.int32, device=dev)
+    sin_table = torch.empty(max(lens), HEAD_DIM // 2, dtype=torch.float32, device=dev)
+    cos_table = torch.empty_like(sin_table)
+    gqa.sin_cos_cache(sin_table, cos_table, HEAD_DIM)
     lens_dev = torch.tensor(lens, dtype=torch.int32, device=dev)
     workspace = gqa.binding.workspace_for(batch, hq, hkv, dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -286,8 +289,10 @@ def run_ours(args) -> None:
                            workspace_bytes=workspace.numel() * 4)
 
     def attention(slot: int) -> None:
+        # Ahead of each attention call are the front stage (writes the newest rows only) and
+        # the previous layer's kernels (other caches): older rows may be prefetched early.
         kw = dict(num_kv_heads=hkv, layout=layout, seq_lens=lens, workspace=workspace,
-                  status=status)
+                  status=status, early_prefetch=True)
         if paged:
             kw.update(seq_lens_dev=lens_dev, block_table=tables[slot])
         else:
@@ -303,7 +308,8 @@ def run_ours(args) -> None:
             kw = dict(block_table=tables[slot], positions_dev=positions_dev) if paged else dict(
                 fixed_block=slot)
             gqa.qk_norm_rope_append(q_raw, k_new, v_new, weight, k_pool, v_pool, layout=layout,
-                                    positions=positions, q_out=q_rot, **kw)
+                                    positions=positions, q_out=q_rot, sin_cache=sin_table,
+                                    cos_cache=cos_table, **kw)
         attention(slot)
 
     def barrier() -> None:

@@ -99,6 +99,13 @@ int gqa_layout_pool(int32_t num_blocks, int32_t block_tokens, int32_t num_kv_hea
  *                   output depends on (length, split_keys) only, never on batch size, head
  *                   count or rank count, so equal split_keys give bit-equal results.
  *   max_ctas        0 = one CTA per SM; otherwise an upper bound on the grid.
+ *   early_prefetch  0 = start reading the cache only when all earlier work of the stream has
+ *                   finished. 1 = the caller promises that work still running ahead of this
+ *                   call in the stream writes no cache row other than the newest position
+ *                   (seq_len - 1) of each sequence and changes neither seq_lens_dev nor the
+ *                   block table; K/V rows of older positions are then requested while that
+ *                   work is still finishing (the reference's decode step satisfies this: its
+ *                   QKV GEMV and QK-Norm write the row of `pos` only).
  *   status_dev      optional device int32, set non-zero by a kernel whose bounded wait ran
  *                   out (it then skips its work instead of hanging).
  *   stream          cudaStream_t (null = default stream), as the reference passes it.
@@ -114,6 +121,8 @@ typedef struct gqa_decode_params {
     int32_t split_keys;
     int32_t max_ctas;
     int32_t plan_len_hint;
+    int32_t early_prefetch;
+    int32_t reserved;
     gqa_kv_layout layout;
     const void* q;
     const void* k_cache;

@@ -49,6 +49,8 @@ class _DecodeParams(C.Structure):
         ("split_keys", C.c_int32),
         ("max_ctas", C.c_int32),
         ("plan_len_hint", C.c_int32),
+        ("early_prefetch", C.c_int32),
+        ("reserved", C.c_int32),
         ("layout", _Layout),
         ("q", C.c_void_p),
         ("k_cache", C.c_void_p),
@@ -228,7 +230,7 @@ def _int_array(values: Optional[Sequence[int]]):
 
 def _decode_params(q, k_cache, v_cache, out, layout, seq_lens_host, seq_lens_dev, block_table,
                    fixed_block, workspace, split_keys, max_ctas, plan_len_hint, status, stream,
-                   keep):
+                   keep, early_prefetch=False):
     batch, hq, d = q.shape
     p = _DecodeParams()
     p.dtype = _dtype_code(q)
@@ -239,6 +241,7 @@ def _decode_params(q, k_cache, v_cache, out, layout, seq_lens_host, seq_lens_dev
     p.split_keys = split_keys
     p.max_ctas = max_ctas
     p.plan_len_hint = plan_len_hint
+    p.early_prefetch = 1 if early_prefetch else 0
     p.layout = layout.c()
     p.q, p.k_cache, p.v_cache, p.out = _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out)
     p.workspace = _ptr(workspace)
@@ -284,14 +287,14 @@ def decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: t
            block_table: Optional[torch.Tensor] = None, fixed_block: int = 0,
            workspace: Optional[torch.Tensor] = None, split_keys: int = 0, max_ctas: int = 0,
            plan_len_hint: int = 0, status: Optional[torch.Tensor] = None,
-           stream: Optional[int] = None) -> None:
+           stream: Optional[int] = None, early_prefetch: bool = False) -> None:
     """Decode attention for q [batch, num_q_heads, 128] on the current stream (or `stream`)."""
     if stream is None:
         stream = torch.cuda.current_stream().cuda_stream
     keep = {"num_kv_heads": num_kv_heads}
     p = _decode_params(q, k_cache, v_cache, out, layout, seq_lens, seq_lens_dev, block_table,
                        fixed_block, workspace, split_keys, max_ctas, plan_len_hint, status,
-                       stream, keep)
+                       stream, keep, early_prefetch)
     _check(lib().gqa_decode(C.byref(p)), "gqa_decode")
 
 
@@ -473,5 +476,6 @@ def decode_sharded(comm: ShardComm, gathered: torch.Tensor, q, k_cache, v_cache,
     p = _decode_params(q, k_cache, v_cache, out, layout, kw.get("seq_lens"),
                        kw.get("seq_lens_dev"), kw.get("block_table"), kw.get("fixed_block", 0),
                        kw.get("workspace"), kw.get("split_keys", 0), kw.get("max_ctas", 0),
-                       kw.get("plan_len_hint", 0), kw.get("status"), stream, keep)
+                       kw.get("plan_len_hint", 0), kw.get("status"), stream, keep,
+                       kw.get("early_prefetch", False))
     _check(lib().gqa_decode_sharded(C.byref(p), comm._h, _ptr(gathered)), "gqa_decode_sharded")

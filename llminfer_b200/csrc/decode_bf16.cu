@@ -56,6 +56,7 @@ struct Cursor {
     int32_t item;
     int32_t k;
     int32_t k_end;
+    int32_t k_last;  // stage holding the newest position of the sequence
     int32_t b;
     int32_t hk;
     bool valid;
@@ -84,6 +85,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    timeline_mark(0);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < WARPS * STAGES; ++i) mbar_init(smem_u32(&s_bar[i]), 1);
@@ -91,10 +93,16 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
         prefetch_tensormap(&tmap_k);
         prefetch_tensormap(&tmap_v);
     }
-    // Everything above overlaps the previous kernel of the stream; from here on its results
-    // (the rotated query, the appended K/V rows, the lengths) are read.
-    pdl_wait();
+    // The next kernel of the stream may be scheduled from now on (it waits for this one's
+    // results itself before it reads them).
     pdl_launch_dependents();
+    // Everything up to pdl_wait() overlaps the previous kernel of the stream. With
+    // a.early_prefetch the caller has promised that nothing still running ahead of this
+    // kernel writes cache rows other than the newest position of each sequence, nor the
+    // lengths or the block table: stages that do not hold a newest position are then
+    // requested before the wait, which hides the DRAM ramp behind the predecessor's tail.
+    if (!a.early_prefetch) pdl_wait();
+    timeline_mark(1);
     const WorkTables tables = build_work_tables(a, s_tables);
     __syncthreads();
 
@@ -104,11 +112,12 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     const uint32_t ring = smem_u32(ring_all + warp * STAGES * kStageBytes);
     const uint32_t bars = smem_u32(&s_bar[warp * STAGES]);
 
-    // ---- producer side: this warp's chunk sequence across the CTA's items ---------------
+    // ---- producer side: this warp's stage sequence across the CTA's items ----------------
     Cursor prod;
     prod.item = blockIdx.x - gridDim.x;
     prod.k = 0;
     prod.k_end = 0;
+    prod.k_last = 0;
     prod.b = 0;
     prod.hk = 0;
     prod.valid = true;
@@ -123,6 +132,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                 c.hk = it.hk;
                 c.k = it.chunk_begin * kChunkKeys / KEYS + warp;
                 c.k_end = ceil_div(min(it.len, it.chunk_end * kChunkKeys), KEYS);
+                c.k_last = (it.len - 1) / KEYS;
             }
         }
     };
@@ -157,8 +167,16 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
         prod.k += WARPS;
         normalize(prod);
     };
+    if (a.early_prefetch) {
 #pragma unroll 1
-    for (int s = 0; s < STAGES; ++s) issue();
+        for (int s = 0; s < STAGES; ++s) {
+            if (!prod.valid || prod.k == prod.k_last) break;
+            issue();
+        }
+        pdl_wait();
+    }
+#pragma unroll 1
+    for (int s = (int)produced; s < STAGES; ++s) issue();
 
     // ---- per-lane constants of the fragment loads ----------------------------------------
     const int r8 = lane & 7;
@@ -203,9 +221,9 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
             o[dt][0] = 0.0f; o[dt][1] = 0.0f; o[dt][2] = 0.0f; o[dt][3] = 0.0f;
         }
 
-#pragma unroll 1
         const int32_t key_end = min(it.len, it.chunk_end * kChunkKeys);
         const int32_t k_end = ceil_div(key_end, KEYS);
+#pragma unroll 1
         for (int32_t k = it.chunk_begin * kChunkKeys / KEYS + warp; k < k_end; k += WARPS) {
             if (dead) break;
             const uint32_t stage = consumed % STAGES;
@@ -214,6 +232,11 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                 dead = true;
                 if (lane == 0 && a.status != nullptr) atomicExch(a.status, 1);
                 break;
+            }
+            if (consumed == 0) {
+                timeline_mark(2);
+                timeline_cta(0);
+                timeline_cta(1);
             }
             const uint32_t kbase = ring + stage * kStageBytes;
             const uint32_t vbase = kbase + kTileBytes;
@@ -326,6 +349,8 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
         }
 
         // ---- merge the warps of this CTA ---------------------------------------------------
+        timeline_mark(3);
+        timeline_cta(2);
 #pragma unroll
         for (int d = 4; d < 32; d <<= 1) {
             l0 += __shfl_xor_sync(0xffffffffu, l0, d);
@@ -380,7 +405,29 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
         }
         __syncthreads();
     }
+    timeline_mark(4);
+    timeline_cta(3);
 }
+
+#ifdef GQA_TIMELINE
+__device__ unsigned long long g_timeline[64];
+__device__ unsigned long long g_cta_marks[4 * 1024];
+extern "C" int gqa_timeline_ctas(unsigned long long* host) {
+    return cudaMemcpyFromSymbol(host, g_cta_marks, sizeof(unsigned long long) * 4096) ==
+                   cudaSuccess ? 0 : -1;
+}
+extern "C" int gqa_timeline_read(unsigned long long* host64, int reset) {
+    if (cudaMemcpyFromSymbol(host64, g_timeline, sizeof(unsigned long long) * 64) != cudaSuccess) {
+        return -1;
+    }
+    if (reset) {
+        unsigned long long init[64];
+        for (int i = 0; i < 64; ++i) init[i] = (i & 1) ? 0ull : ~0ull;
+        if (cudaMemcpyToSymbol(g_timeline, init, sizeof(init)) != cudaSuccess) return -1;
+    }
+    return 0;
+}
+#endif
 
 size_t stream_bf16_smem_bytes(int warps, int stages, int keys, int batch_for_tables) {
     size_t bytes = 1024;  // alignment slack

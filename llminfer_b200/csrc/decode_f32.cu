@@ -58,8 +58,8 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const WorkTables tables = build_work_tables(a, s_tables);
     const int32_t n_items = total_items(a, tables);
     const int32_t group = a.group;
@@ -181,39 +181,27 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
     }
 }
 
-constexpr int kCombineTile = 256;  // splits merged per pass
+constexpr int kCombineTile = 32;  // splits merged per pass
 
-// Block-wide reductions over 128 threads in a fixed order (so results are reproducible).
-__device__ __forceinline__ float block_max_128(float v, float* scratch) {
-    v = warp_max(v);
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    __syncthreads();
-    const float r = fmaxf(fmaxf(scratch[0], scratch[1]), fmaxf(scratch[2], scratch[3]));
-    __syncthreads();
-    return r;
-}
-
-__device__ __forceinline__ float block_sum_128(float v, float* scratch) {
-    v = warp_sum(v);
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    __syncthreads();
-    const float r = (scratch[0] + scratch[1]) + (scratch[2] + scratch[3]);
-    __syncthreads();
-    return r;
-}
-
-// One CTA per (sequence, query head), thread d owns output channel d. Partial records are
-// read with L1-bypassing loads: they were written by the kernel this one overlaps with. The m and l of up to
-// kCombineTile splits are fetched in parallel and turned into weights in shared memory, then
-// the O rows are accumulated with independent loads; longer split lists are folded tile by
-// tile with a running (M, L).
-template <bool BF16_OUT>
-__global__ void __launch_bounds__(kHeadDim) gqa_decode_combine(const DecodeArgs a) {
+// One CTA per (sequence, query head) with LANES threads per output channel. Thread (lane j,
+// channel d) owns splits j, j + LANES, ... of the pass: every load of a pass (O rows, m and l)
+// is issued before any is used, so a pass costs one trip to L2 whatever the split count up to
+// 32; longer split lists fold pass by pass with a running (M, L). Small grids use 8 lanes
+// (1024 threads); grids that would not fit the GPU in one wave at that size use 2. Sums run in a fixed order, so results are reproducible.
+// Partial records are read with L1-bypassing loads: the kernel that wrote them may still have
+// been running when this one started.
+template <bool BF16_OUT, int LANES>
+__global__ void __launch_bounds__(kHeadDim * LANES) gqa_decode_combine(const DecodeArgs a) {
+    constexpr int kCombineLanes = LANES;
+    constexpr int kCombinePerLane = kCombineTile / LANES;
     extern __shared__ int32_t s_tables[];
-    __shared__ float s_w[kCombineTile];
-    __shared__ float s_scratch[4];
-    pdl_wait();
+    __shared__ float s_m[kCombineTile];
+    __shared__ float s_l[kCombineTile];
+    __shared__ float s_part[kCombineLanes][kHeadDim];
+    timeline_mark(5);
     pdl_launch_dependents();
+    pdl_wait();
+    timeline_mark(6);
     const WorkTables tables = build_work_tables(a, s_tables);
     const int32_t b = blockIdx.x / a.num_q_heads;
     const int32_t h = blockIdx.x - b * a.num_q_heads;
@@ -224,7 +212,8 @@ __global__ void __launch_bounds__(kHeadDim) gqa_decode_combine(const DecodeArgs 
     unit_items(a, tables, b, hk, &first, &nsplits);
     if (nsplits <= 1) return;  // the streaming kernel already wrote the final output
 
-    const int d = threadIdx.x;
+    const int d = threadIdx.x & (kHeadDim - 1);
+    const int j = threadIdx.x >> 7;
     const int64_t rec_floats = (int64_t)group * (kHeadDim + 2);
     const float* rec0 = a.workspace + (int64_t)first * rec_floats;
     const float* m_base = rec0 + group * kHeadDim + n;
@@ -234,54 +223,66 @@ __global__ void __launch_bounds__(kHeadDim) gqa_decode_combine(const DecodeArgs 
     float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
     for (int32_t base = 0; base < nsplits; base += kCombineTile) {
         const int32_t cnt = min(kCombineTile, nsplits - base);
-        float mv[kCombineTile / kHeadDim], lv[kCombineTile / kHeadDim];
-        float tmax = -INFINITY;
+        float o[kCombinePerLane];
+        float ml[kCombinePerLane];
 #pragma unroll
-        for (int j = 0; j < kCombineTile / kHeadDim; ++j) {
-            const int32_t s = d + j * kHeadDim;
-            mv[j] = -INFINITY;
-            lv[j] = 0.f;
+        for (int r = 0; r < kCombinePerLane; ++r) {
+            const int32_t s = j + r * kCombineLanes;
+            o[r] = 0.f;
+            ml[r] = 0.f;
             if (s < cnt) {
-                mv[j] = __ldcg(m_base + (int64_t)(base + s) * rec_floats);
-                lv[j] = __ldcg(l_base + (int64_t)(base + s) * rec_floats);
+                const int64_t off = (int64_t)(base + s) * rec_floats;
+                o[r] = __ldcg(o_base + off);
+                if (d == 0) ml[r] = __ldcg(m_base + off);
+                if (d == 1) ml[r] = __ldcg(l_base + off);
             }
-            tmax = fmaxf(tmax, mv[j]);
         }
-        tmax = block_max_128(tmax, s_scratch);
+        if (d < 2) {
+#pragma unroll
+            for (int r = 0; r < kCombinePerLane; ++r) {
+                const int32_t s = j + r * kCombineLanes;
+                if (s < cnt) (d == 0 ? s_m : s_l)[s] = ml[r];
+            }
+        }
+        __syncthreads();
+        float tmax = s_m[0];
+        for (int32_t i = 1; i < cnt; ++i) tmax = fmaxf(tmax, s_m[i]);
         const float m_new = fmaxf(m_run, tmax);
         const float rescale = BF16_OUT ? ex2_approx(m_run - m_new) : exp2f(m_run - m_new);
-        float lpart = 0.f;
-#pragma unroll
-        for (int j = 0; j < kCombineTile / kHeadDim; ++j) {
-            const int32_t s = d + j * kHeadDim;
-            const float w = BF16_OUT ? ex2_approx(mv[j] - m_new) : exp2f(mv[j] - m_new);
-            if (s < cnt) s_w[s] = w;
-            lpart += lv[j] * w;
+        float ltile = 0.f;
+        for (int32_t i = 0; i < cnt; ++i) {
+            const float w = BF16_OUT ? ex2_approx(s_m[i] - m_new) : exp2f(s_m[i] - m_new);
+            ltile += s_l[i] * w;
         }
-        const float ltile = block_sum_128(lpart, s_scratch);  // also publishes s_w
-        float part[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        const float* o_tile = o_base + (int64_t)base * rec_floats;
-        int32_t s = 0;
-        for (; s + 8 <= cnt; s += 8) {
-            float v[8];
+        float part = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __ldcg(o_tile + (int64_t)(s + j) * rec_floats);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) part[j] += v[j] * s_w[s + j];
+        for (int r = 0; r < kCombinePerLane; ++r) {
+            const int32_t s = j + r * kCombineLanes;
+            if (s < cnt) {
+                const float w = BF16_OUT ? ex2_approx(s_m[s] - m_new) : exp2f(s_m[s] - m_new);
+                part += o[r] * w;
+            }
         }
-        for (; s < cnt; ++s) part[0] += __ldcg(o_tile + (int64_t)s * rec_floats) * s_w[s];
-        const float tile_acc = ((part[0] + part[1]) + (part[2] + part[3])) +
-                               ((part[4] + part[5]) + (part[6] + part[7]));
-        acc = acc * rescale + tile_acc;
+        s_part[j][d] = part;
+        __syncthreads();
+        if (j == 0) {
+            float tile_acc = s_part[0][d];
+#pragma unroll
+            for (int jj = 1; jj < kCombineLanes; ++jj) tile_acc += s_part[jj][d];
+            acc = acc * rescale + tile_acc;
+        }
         l_run = l_run * rescale + ltile;
         m_run = m_new;
-        __syncthreads();  // s_w is rewritten by the next tile
+        __syncthreads();  // the next pass overwrites s_m, s_l and s_part
     }
-    const int64_t o_idx = ((int64_t)b * a.num_q_heads + h) * kHeadDim + d;
-    if (BF16_OUT) {
-        reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(acc / l_run);
-    } else {
-        reinterpret_cast<float*>(a.out)[o_idx] = acc / l_run;
+    timeline_mark(7);
+    if (j == 0) {
+        const int64_t o_idx = ((int64_t)b * a.num_q_heads + h) * kHeadDim + d;
+        if (BF16_OUT) {
+            reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(acc / l_run);
+        } else {
+            reinterpret_cast<float*>(a.out)[o_idx] = acc / l_run;
+        }
     }
 }
 
@@ -300,10 +301,17 @@ cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t s
     const size_t smem =
         args.seq_lens_dev != nullptr ? 2 * ((size_t)args.batch + 1) * sizeof(int32_t) : 0;
     const int grid = args.batch * args.num_q_heads;
+    const bool wide = grid <= 160;
     if (bf16_out) {
-        return launch_pdl(gqa_decode_combine<true>, dim3(grid), dim3(kHeadDim), smem, stream, args);
+        return wide ? launch_pdl(gqa_decode_combine<true, 8>, dim3(grid), dim3(kHeadDim * 8), smem,
+                                 stream, args)
+                    : launch_pdl(gqa_decode_combine<true, 2>, dim3(grid), dim3(kHeadDim * 2), smem,
+                                 stream, args);
     }
-    return launch_pdl(gqa_decode_combine<false>, dim3(grid), dim3(kHeadDim), smem, stream, args);
+    return wide ? launch_pdl(gqa_decode_combine<false, 8>, dim3(grid), dim3(kHeadDim * 8), smem,
+                             stream, args)
+                : launch_pdl(gqa_decode_combine<false, 2>, dim3(grid), dim3(kHeadDim * 2), smem,
+                             stream, args);
 }
 
 }  // namespace gqa

@@ -40,8 +40,8 @@ __global__ void __launch_bounds__(kFrontWarps * 32) qk_norm_rope_append_kernel(c
     const int b = blockIdx.y;
     const int row = blockIdx.x * kFrontWarps + warp;
     const int n_rows = f.num_q_heads + (f.v_new != nullptr ? 2 : 1) * f.num_kv_heads;
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     if (row >= n_rows) return;
 
     const int32_t pos = f.positions_dev != nullptr ? f.positions_dev[b] : f.uniform_pos;

@@ -477,6 +477,7 @@ int gqa_decode(const gqa_decode_params* p) {
     a.blocks_per_seq = p->blocks_per_seq;
     a.block_tokens = p->layout.block_tokens;
     a.fixed_block = p->fixed_block;
+    a.early_prefetch = p->early_prefetch ? 1 : 0;
     a.scale_log2 = (1.0f / sqrtf((float)kHeadDim)) * 1.44269504088896340736f;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(p->stream);
 

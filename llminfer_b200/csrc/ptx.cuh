@@ -145,4 +145,36 @@ __device__ __forceinline__ void pdl_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// Optional device-side timeline for tuning builds (-DGQA_TIMELINE): every mark keeps the
+// earliest and the latest %globaltimer value seen at that point of a launch. Compiles to
+// nothing otherwise.
+#ifdef GQA_TIMELINE
+extern __device__ unsigned long long g_timeline[64];
+extern __device__ unsigned long long g_cta_marks[4 * 1024];  // per CTA: smid, first data, merge, end
+__device__ __forceinline__ void timeline_cta(int field) {
+    if (threadIdx.x == 0 && blockIdx.x < 1024) {
+        unsigned long long t;
+        if (field == 0) {
+            unsigned int smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            t = smid;
+        } else {
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        }
+        g_cta_marks[4 * blockIdx.x + field] = t;
+    }
+}
+__device__ __forceinline__ void timeline_mark(int slot) {
+    if ((threadIdx.x & 31) == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        atomicMin(&g_timeline[2 * slot], t);
+        atomicMax(&g_timeline[2 * slot + 1], t);
+    }
+}
+#else
+__device__ __forceinline__ void timeline_mark(int) {}
+__device__ __forceinline__ void timeline_cta(int) {}
+#endif
+
 }  // namespace gqa

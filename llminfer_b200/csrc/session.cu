@@ -26,6 +26,8 @@ struct gqa_session {
     size_t gather_bytes;
     void* workspace;
     size_t workspace_bytes;
+    float* sin_table;  // [max_seq_len, head_dim / 2], built once at creation
+    float* cos_table;
 };
 
 namespace {
@@ -47,6 +49,8 @@ void release(gqa_session* s) {
     if (s->dev_in) cudaFree(s->dev_in);
     if (s->dev_out) cudaFree(s->dev_out);
     if (s->workspace) cudaFree(s->workspace);
+    if (s->sin_table) cudaFree(s->sin_table);
+    if (s->cos_table) cudaFree(s->cos_table);
     if (s->stream) cudaStreamDestroy(s->stream);
     delete s;
 }
@@ -88,6 +92,12 @@ int gqa_session_create(int32_t dtype, int32_t max_batch, int32_t num_q_heads,
     ok = ok && cudaMalloc(&s->dev_in, s->in_bytes) == cudaSuccess;
     ok = ok && cudaMalloc(&s->dev_out, q_bytes(s, max_batch)) == cudaSuccess;
     ok = ok && cudaMalloc(&s->workspace, s->workspace_bytes) == cudaSuccess;
+    const size_t table_bytes = (size_t)max_seq_len * (head_dim / 2) * sizeof(float);
+    ok = ok && cudaMalloc(&s->sin_table, table_bytes) == cudaSuccess;
+    ok = ok && cudaMalloc(&s->cos_table, table_bytes) == cudaSuccess;
+    ok = ok && gqa_sin_cos_cache(s->sin_table, s->cos_table, head_dim, max_seq_len, s->stream) ==
+                   GQA_OK;
+    ok = ok && cudaStreamSynchronize(s->stream) == cudaSuccess;
     if (!ok) {
         release(s);
         return GQA_ERR_CUDA;
@@ -146,6 +156,9 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     f.k_new = s->dev_in + off_k;
     f.v_new = s->dev_in + off_v;
     f.qk_weight = qk_weight_dev;
+    f.sin_cache = s->sin_table;
+    f.cos_cache = s->cos_table;
+    f.table_len = s->max_seq_len;
     f.k_cache = k_cache;
     f.v_cache = v_cache;
     f.positions_host = poss;
@@ -175,6 +188,9 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     p.seq_lens_dev = reinterpret_cast<const int32_t*>(s->dev_in + off_len);
     p.block_table_dev = block_table_dev;
     p.stream = s->stream;
+    // Ahead of the attention in this stream are the H2D copy of the new rows and the front
+    // stage, which writes the cache rows of the new positions only.
+    p.early_prefetch = 1;
     rc = gqa_decode(&p);
     if (rc != GQA_OK) return rc;
 

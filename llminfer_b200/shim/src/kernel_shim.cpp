@@ -84,6 +84,10 @@ void mha_kernel_cu(const tensor::Tensor& query, const tensor::Tensor& key_cache,
     const int32_t seq_len = pos + 1;
     p.seq_lens_host = &seq_len;
     p.stream = stream;
+    // In the reference's decode step the kernels ahead of attention (QKV GEMV, QK-Norm + RoPE)
+    // write the cache row of `pos` only (code/source/model/qwen3_fused.cpp:517-533), so older
+    // rows may be fetched while they finish.
+    p.early_prefetch = 1;
     require_ok(gqa_decode(&p), "gqa_decode");
 }
 

@@ -29,7 +29,7 @@ def gqa(built_lib):
 
 
 def run_reference_layout(gqa, q_bits, k_bits, v_bits, *, hkv, layer_id, length, split_keys=0,
-                         max_ctas=0):
+                         max_ctas=0, early_prefetch=False):
     layers, max_seq_len, _ = k_bits.shape
     hq = q_bits.shape[0]
     layout = gqa.layout_reference(layers, max_seq_len, hkv)
@@ -41,7 +41,7 @@ def run_reference_layout(gqa, q_bits, k_bits, v_bits, *, hkv, layer_id, length, 
     status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
     gqa.decode(q, k, v, out, num_kv_heads=hkv, layout=layout, seq_lens=[length],
                fixed_block=layer_id, workspace=ws, split_keys=split_keys, max_ctas=max_ctas,
-               status=status)
+               status=status, early_prefetch=early_prefetch)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     return H.bits_of(out)[0]
@@ -55,6 +55,10 @@ def test_bf16_golden_cases(gqa, index, request):
     k[layer_id, length:] = H.NAN_BITS
     v[layer_id, length:] = H.NAN_BITS
     got_bits = run_reference_layout(gqa, q, k, v, hkv=hkv, layer_id=layer_id, length=length)
+    # Requesting old rows before earlier work has finished changes timing, never values.
+    early = run_reference_layout(gqa, q, k, v, hkv=hkv, layer_id=layer_id, length=length,
+                                 early_prefetch=True)
+    assert np.array_equal(got_bits, early)
     got = cases.bf16_bits_to_f32(got_bits)
     want = H.oracle_reference_layout(q, k, v, layer_id=layer_id, length=length, hkv=hkv,
                                      max_seq_len=max_seq_len)
@@ -239,6 +243,43 @@ def test_f32_lengths_and_groups(gqa, length, group):
                seq_lens=[length], fixed_block=1, workspace=ws)
     _, rel_err = H.errors(H.f32_of(out)[0], want)
     assert rel_err <= REL_TOL_F32, rel_err
+
+
+def test_bf16_decode_steps_with_early_prefetch(gqa):
+    """A run of decode steps (front stage appends a row, attention reads the cache) queued
+    back to back on one stream with early prefetch: every step must see the row appended just
+    before it, and only that one."""
+    rng = np.random.default_rng(43)
+    hq, hkv, max_seq_len, start, steps = 32, 8, 640, 250, 140
+    layout = gqa.layout_reference(1, max_seq_len, hkv)
+    k_hist = H.rand_bits(rng, (1, max_seq_len, hkv * H.D))
+    v_hist = H.rand_bits(rng, (1, max_seq_len, hkv * H.D))
+    k_hist[0, start:] = H.NAN_BITS
+    v_hist[0, start:] = H.NAN_BITS
+    w = cases.to_bf16_bits(1.0 + 0.05 * rng.standard_normal(256, dtype=np.float32))
+    q_all = H.rand_bits(rng, (steps, 1, hq, H.D))
+    k_all = H.rand_bits(rng, (steps, 1, hkv, H.D))
+    v_all = H.rand_bits(rng, (steps, 1, hkv, H.D))
+    dk, dv, dw = H.bf16_tensor(k_hist), H.bf16_tensor(v_hist), H.bf16_tensor(w)
+    dq, dkn, dvn = H.bf16_tensor(q_all), H.bf16_tensor(k_all), H.bf16_tensor(v_all)
+    outs = torch.zeros(steps, 1, hq, H.D, dtype=torch.bfloat16, device="cuda:0")
+    ws = gqa.binding.workspace_for(1, hq, hkv, "cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    for i in range(steps):
+        pos = start + i
+        gqa.qk_norm_rope_append(dq[i], dkn[i], dvn[i], dw, dk, dv, layout=layout, positions=[pos])
+        gqa.decode(dq[i], dk, dv, outs[i], num_kv_heads=hkv, layout=layout, seq_lens=[pos + 1],
+                   workspace=ws, status=status, early_prefetch=True)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    k_final, v_final, q_rot = H.bits_of(dk), H.bits_of(dv), H.bits_of(dq)
+    got = H.f32_of(outs)
+    for i in (0, 1, 5, 37, 70, 71, 72, steps - 1):
+        pos = start + i
+        want = H.oracle_reference_layout(q_rot[i, 0], k_final, v_final, layer_id=0, length=pos + 1,
+                                         hkv=hkv, max_seq_len=max_seq_len)
+        abs_err, rel_err = H.errors(got[i, 0], want)
+        assert abs_err <= ABS_TOL_BF16 and rel_err <= REL_TOL_BF16, (i, abs_err, rel_err)
 
 
 def test_bf16_long_context_properties(gqa):
