@@ -85,7 +85,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    timeline_mark(0);
+    timeline_mark(0, a.fixed_block);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < WARPS * STAGES; ++i) mbar_init(smem_u32(&s_bar[i]), 1);
@@ -102,7 +102,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     // lengths or the block table: stages that do not hold a newest position are then
     // requested before the wait, which hides the DRAM ramp behind the predecessor's tail.
     if (!a.early_prefetch) pdl_wait();
-    timeline_mark(1);
+    timeline_mark(1, a.fixed_block);
     const WorkTables tables = build_work_tables(a, s_tables);
     __syncthreads();
 
@@ -234,7 +234,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                 break;
             }
             if (consumed == 0) {
-                timeline_mark(2);
+                timeline_mark(2, a.fixed_block);
                 timeline_cta(0);
                 timeline_cta(1);
             }
@@ -349,7 +349,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
         }
 
         // ---- merge the warps of this CTA ---------------------------------------------------
-        timeline_mark(3);
+        timeline_mark(3, a.fixed_block);
         timeline_cta(2);
 #pragma unroll
         for (int d = 4; d < 32; d <<= 1) {
@@ -405,7 +405,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
         }
         __syncthreads();
     }
-    timeline_mark(4);
+    timeline_mark(4, a.fixed_block);
     timeline_cta(3);
 }
 

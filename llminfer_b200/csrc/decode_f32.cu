@@ -198,10 +198,10 @@ __global__ void __launch_bounds__(kHeadDim * LANES) gqa_decode_combine(const Dec
     __shared__ float s_m[kCombineTile];
     __shared__ float s_l[kCombineTile];
     __shared__ float s_part[kCombineLanes][kHeadDim];
-    timeline_mark(5);
+    timeline_mark(5, a.fixed_block);
     pdl_launch_dependents();
     pdl_wait();
-    timeline_mark(6);
+    timeline_mark(6, a.fixed_block);
     const WorkTables tables = build_work_tables(a, s_tables);
     const int32_t b = blockIdx.x / a.num_q_heads;
     const int32_t h = blockIdx.x - b * a.num_q_heads;
@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(kHeadDim * LANES) gqa_decode_combine(const Dec
         m_run = m_new;
         __syncthreads();  // the next pass overwrites s_m, s_l and s_part
     }
-    timeline_mark(7);
+    timeline_mark(7, a.fixed_block);
     if (j == 0) {
         const int64_t o_idx = ((int64_t)b * a.num_q_heads + h) * kHeadDim + d;
         if (BF16_OUT) {

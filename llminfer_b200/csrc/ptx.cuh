@@ -146,8 +146,9 @@ __device__ __forceinline__ void pdl_wait() {
 }
 
 // Optional device-side timeline for tuning builds (-DGQA_TIMELINE): every mark keeps the
-// earliest and the latest %globaltimer value seen at that point of a launch. Compiles to
-// nothing otherwise.
+// earliest and the latest %globaltimer value seen at that point of a launch, in one of four
+// banks chosen by `call` (the block index of the launch, so that consecutive layers of a
+// captured graph can be told apart). Compiles to nothing otherwise.
 #ifdef GQA_TIMELINE
 extern __device__ unsigned long long g_timeline[64];
 extern __device__ unsigned long long g_cta_marks[4 * 1024];  // per CTA: smid, first data, merge, end
@@ -164,7 +165,8 @@ __device__ __forceinline__ void timeline_cta(int field) {
         g_cta_marks[4 * blockIdx.x + field] = t;
     }
 }
-__device__ __forceinline__ void timeline_mark(int slot) {
+__device__ __forceinline__ void timeline_mark(int slot, int call) {
+    slot += 8 * (call & 3);
     if ((threadIdx.x & 31) == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -173,7 +175,7 @@ __device__ __forceinline__ void timeline_mark(int slot) {
     }
 }
 #else
-__device__ __forceinline__ void timeline_mark(int) {}
+__device__ __forceinline__ void timeline_mark(int, int) {}
 __device__ __forceinline__ void timeline_cta(int) {}
 #endif
 
