@@ -159,6 +159,25 @@ int gqa_decode_plan(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pla
 /* Launches the attention kernels on p->stream. Asynchronous. */
 int gqa_decode(const gqa_decode_params* p);
 
+/*
+ * No counterpart in the reference (its caller always allocates kv_split_output,
+ * code/source/model/qwen3_fused.cpp:502). The same attention as gqa_decode() for callers that
+ * cannot allocate device memory around the call - code running under stream capture, serving
+ * loops barred from the allocator after start-up, hosts with a fixed memory budget: p->workspace
+ * and p->workspace_bytes are ignored and the split partials go to an array of
+ * GQA_STATIC_SCRATCH_BYTES that lives inside the library (each GPU that loads the library holds
+ * it until the process exits). The call allocates and frees no device memory.
+ *   - The first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *   - A plan that needs more than GQA_STATIC_SCRATCH_BYTES (a very small explicit split_keys
+ *     on a very long context) returns GQA_ERR_WORKSPACE and launches nothing.
+ *   - All calls on one device share the array. Calls that can overlap on the GPU (different
+ *     streams, concurrent graph launches) race on it: serialise them, or use gqa_decode() with
+ *     one workspace each. Nothing in the array has to be cleared between calls.
+ */
+#define GQA_STATIC_SCRATCH_BYTES (8u << 20)
+int gqa_decode_static_scratch(const gqa_decode_params* p);
+
 /* ---- front stage: QK-Norm + RoPE + KV append ------------------------------------------ */
 /*
  * Stands in for kernel::fused_qk_norm_rope_kernel_cu

@@ -13,6 +13,7 @@ from .binding import (  # noqa: F401
     decode,
     decode_plan,
     decode_sharded,
+    decode_static_scratch,
     layout_pool,
     layout_reference,
     lib,

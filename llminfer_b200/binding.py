@@ -113,6 +113,7 @@ _SIGNATURES = {
     "gqa_layout_pool": (C.c_int, [C.c_int32] * 4 + [C.POINTER(_Layout)]),
     "gqa_decode_plan": (C.c_int, [C.POINTER(_DecodeParams), C.c_int32, C.POINTER(_PlanInfo)]),
     "gqa_decode": (C.c_int, [C.POINTER(_DecodeParams)]),
+    "gqa_decode_static_scratch": (C.c_int, [C.POINTER(_DecodeParams)]),
     "gqa_qk_norm_rope_append": (C.c_int, [C.POINTER(_FrontParams)]),
     "gqa_sin_cos_cache": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "gqa_session_create": (C.c_int, [C.c_int32] * 6 + [C.POINTER(C.c_void_p)]),
@@ -296,6 +297,28 @@ def decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: t
                        fixed_block, workspace, split_keys, max_ctas, plan_len_hint, status,
                        stream, keep, early_prefetch)
     _check(lib().gqa_decode(C.byref(p)), "gqa_decode")
+
+
+STATIC_SCRATCH_BYTES = 8 << 20
+
+
+def decode_static_scratch(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                          out: torch.Tensor, *, num_kv_heads: int, layout: KvLayout,
+                          seq_lens: Optional[Sequence[int]] = None,
+                          seq_lens_dev: Optional[torch.Tensor] = None,
+                          block_table: Optional[torch.Tensor] = None, fixed_block: int = 0,
+                          split_keys: int = 0, max_ctas: int = 0, plan_len_hint: int = 0,
+                          status: Optional[torch.Tensor] = None, stream: Optional[int] = None,
+                          early_prefetch: bool = False) -> None:
+    """decode() without a workspace argument: the split scratch is the library's own static
+    device array (for callers that may not allocate device memory); see the header for limits."""
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    keep = {"num_kv_heads": num_kv_heads}
+    p = _decode_params(q, k_cache, v_cache, out, layout, seq_lens, seq_lens_dev, block_table,
+                       fixed_block, None, split_keys, max_ctas, plan_len_hint, status, stream,
+                       keep, early_prefetch)
+    _check(lib().gqa_decode_static_scratch(C.byref(p)), "gqa_decode_static_scratch")
 
 
 def workspace_for(batch: int, num_q_heads: int, num_kv_heads: int, device,

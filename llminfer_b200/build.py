@@ -25,6 +25,7 @@ KERNEL_SOURCES = [
     "csrc/front_stage.cu",
     "csrc/gqa_api.cu",
     "csrc/session.cu",
+    "csrc/static_scratch.cu",
     "csrc/kv_pool.cpp",
     "csrc/shard_comm.cpp",
 ]
