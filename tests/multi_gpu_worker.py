@@ -1,0 +1,100 @@
+"""One rank of the multi-GPU parity check (launched by test_gpu_multi.py with torchrun):
+KV-head-parallel decode through gqa_decode_sharded, gathered over NCCL, compared with the same
+attention computed unsharded on this rank's GPU and with the CPU oracle."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+for p in (ROOT, ROOT / "tests", ROOT / "tests" / "golden"):
+    sys.path.insert(0, str(p))
+
+import cases  # noqa: E402
+import helpers as H  # noqa: E402
+import llminfer_b200 as gqa  # noqa: E402
+from llminfer_b200 import sharding  # noqa: E402
+from oracle import oracle  # noqa: E402
+
+
+def main() -> None:
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    ident = [gqa.ShardComm.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ident, src=0)
+    comm = gqa.ShardComm(ident[0], world, rank)
+
+    hq, hkv, batch, block_tokens, d = 64, 8, 3, 256, 128
+    lens = [3000, 257, 1024]
+    rng = np.random.default_rng(53)  # identical data on every rank
+    blocks_per_seq = 12
+    num_blocks = batch * blocks_per_seq
+    table = rng.permutation(num_blocks).reshape(batch, blocks_per_seq).astype(np.int32)
+    q = H.rand_bits(rng, (batch, hq, d))
+    k_pool = H.rand_bits(rng, (num_blocks, hkv, block_tokens, d))
+    v_pool = H.rand_bits(rng, (num_blocks, hkv, block_tokens, d))
+
+    def run(q_bits, k_bits, v_bits, heads_q, heads_kv, sharded):
+        layout = gqa.layout_pool(num_blocks, block_tokens, heads_kv)
+        dq = H.bf16_tensor(q_bits, dev)
+        dk, dv = H.bf16_tensor(k_bits, dev), H.bf16_tensor(v_bits, dev)
+        out = torch.zeros(batch, heads_q, d, dtype=torch.bfloat16, device=dev)
+        ws = gqa.binding.workspace_for(batch, heads_q, heads_kv, dev)
+        kw = dict(num_kv_heads=heads_kv, layout=layout, seq_lens=lens,
+                  seq_lens_dev=torch.tensor(lens, dtype=torch.int32, device=dev),
+                  block_table=torch.from_numpy(table).to(dev), workspace=ws, split_keys=512)
+        if not sharded:
+            gqa.decode(dq, dk, dv, out, **kw)
+            torch.cuda.synchronize()
+            return out
+        gathered = torch.zeros(world, batch, heads_q, d, dtype=torch.bfloat16, device=dev)
+        gqa.decode_sharded(comm, gathered, dq, dk, dv, out, **kw)
+        torch.cuda.synchronize()
+        return sharding.unshard_output(gathered)
+
+    full = run(q, k_pool, v_pool, hq, hkv, sharded=False)
+    per_q, per_kv = hq // world, hkv // world
+    q_l = q[:, rank * per_q:(rank + 1) * per_q]
+    k_l = np.ascontiguousarray(k_pool[:, rank * per_kv:(rank + 1) * per_kv])
+    v_l = np.ascontiguousarray(v_pool[:, rank * per_kv:(rank + 1) * per_kv])
+    whole = run(q_l, k_l, v_l, per_q, per_kv, sharded=True)
+    # Same split size per head, so the sharded result is bit-equal to the unsharded one.
+    assert torch.equal(whole.view(torch.int16), full.view(torch.int16)), "sharded != unsharded"
+    want = oracle.gqa_decode(q, k_pool.reshape(-1), v_pool.reshape(-1), lens, hkv=hkv,
+                             stride_block=hkv * block_tokens * d, stride_token=d,
+                             stride_head=block_tokens * d, block_tokens=block_tokens,
+                             block_table=table)
+    abs_err, rel_err = H.errors(whole.float().cpu().numpy(), want)
+    assert abs_err <= 2e-2 and rel_err <= 1e-2, (abs_err, rel_err)
+
+    # The host-buffer step with the gather inside.
+    layout_l = gqa.layout_pool(num_blocks, block_tokens, per_kv)
+    session = gqa.Session(batch, per_q, per_kv, blocks_per_seq * block_tokens)
+    pin = lambda bits: torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).view(torch.bfloat16).pin_memory()
+    k_new, v_new = H.rand_bits(rng, (batch, hkv, d)), H.rand_bits(rng, (batch, hkv, d))
+    w = cases.to_bf16_bits(1.0 + 0.05 * rng.standard_normal(256, dtype=np.float32))
+    out_host = torch.zeros(world, batch, per_q, d, dtype=torch.bfloat16).pin_memory()
+    dk, dv = H.bf16_tensor(k_l, dev), H.bf16_tensor(v_l, dev)
+    session.step(pin(q_l), pin(k_new[:, rank * per_kv:(rank + 1) * per_kv]),
+                 pin(v_new[:, rank * per_kv:(rank + 1) * per_kv]), H.bf16_tensor(w, dev), dk, dv,
+                 layout_l, lens, out_host, block_table=torch.from_numpy(table).to(dev), comm=comm)
+    session.close()
+    gathered_bits = out_host.view(torch.int16).numpy().view(np.uint16)
+    all_bits = [None] * world
+    dist.all_gather_object(all_bits, gathered_bits.tobytes())
+    assert all(b == all_bits[0] for b in all_bits), "ranks disagree on the gathered output"
+    assert np.isfinite(out_host.float().numpy()).all()
+
+    comm.close()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("multi_gpu_worker ok")
+
+
+if __name__ == "__main__":
+    main()
