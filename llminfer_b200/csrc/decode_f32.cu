@@ -181,23 +181,26 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
     }
 }
 
-constexpr int kCombineTile = 32;  // splits merged per pass
+constexpr int kCombineTile = 32;   // splits merged per pass
+constexpr int kCombineSlots = 8;   // partial sums per channel per pass, whatever the CTA width
 
-// One CTA per (sequence, query head) with LANES threads per output channel. Thread (lane j,
-// channel d) owns splits j, j + LANES, ... of the pass: every load of a pass (O rows, m and l)
-// is issued before any is used, so a pass costs one trip to L2 whatever the split count up to
-// 32; longer split lists fold pass by pass with a running (M, L). Small grids use 8 lanes
-// (1024 threads); grids that would not fit the GPU in one wave at that size use 2. Sums run in a fixed order, so results are reproducible.
-// Partial records are read with L1-bypassing loads: the kernel that wrote them may still have
-// been running when this one started.
+// One CTA per (sequence, query head) with LANES threads per output channel. The splits of a
+// pass are dealt to 8 slots (split s goes to slot s % 8); a thread owns 8 / LANES slots and
+// adds each slot's splits in ascending order, then the slots are added in ascending order.
+// The result therefore does not depend on LANES, which is only a matter of how many threads
+// share the loads: 8 lanes (1024 threads) for small grids, 2 for grids that would not fit the
+// GPU in one wave at that size. Every load of a pass (O rows, m and l) is issued before any
+// is used, so a pass costs one trip to L2; longer split lists fold pass by pass with a running
+// (M, L). Partial records are read with L1-bypassing loads: the kernel that wrote them may
+// still have been running when this one started.
 template <bool BF16_OUT, int LANES>
 __global__ void __launch_bounds__(kHeadDim * LANES) gqa_decode_combine(const DecodeArgs a) {
-    constexpr int kCombineLanes = LANES;
-    constexpr int kCombinePerLane = kCombineTile / LANES;
+    constexpr int kOwn = kCombineSlots / LANES;            // slots per thread
+    constexpr int kPerSlot = kCombineTile / kCombineSlots;  // splits per slot per pass
     extern __shared__ int32_t s_tables[];
     __shared__ float s_m[kCombineTile];
     __shared__ float s_l[kCombineTile];
-    __shared__ float s_part[kCombineLanes][kHeadDim];
+    __shared__ float s_part[kCombineSlots][kHeadDim];
     timeline_mark(5, a.fixed_block);
     pdl_launch_dependents();
     pdl_wait();
@@ -223,25 +226,31 @@ __global__ void __launch_bounds__(kHeadDim * LANES) gqa_decode_combine(const Dec
     float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
     for (int32_t base = 0; base < nsplits; base += kCombineTile) {
         const int32_t cnt = min(kCombineTile, nsplits - base);
-        float o[kCombinePerLane];
-        float ml[kCombinePerLane];
+        float o[kOwn][kPerSlot];
+        float ml[kOwn][kPerSlot];
 #pragma unroll
-        for (int r = 0; r < kCombinePerLane; ++r) {
-            const int32_t s = j + r * kCombineLanes;
-            o[r] = 0.f;
-            ml[r] = 0.f;
-            if (s < cnt) {
-                const int64_t off = (int64_t)(base + s) * rec_floats;
-                o[r] = __ldcg(o_base + off);
-                if (d == 0) ml[r] = __ldcg(m_base + off);
-                if (d == 1) ml[r] = __ldcg(l_base + off);
+        for (int t = 0; t < kOwn; ++t) {
+#pragma unroll
+            for (int r = 0; r < kPerSlot; ++r) {
+                const int32_t s = (j + t * LANES) + r * kCombineSlots;
+                o[t][r] = 0.f;
+                ml[t][r] = 0.f;
+                if (s < cnt) {
+                    const int64_t off = (int64_t)(base + s) * rec_floats;
+                    o[t][r] = __ldcg(o_base + off);
+                    if (d == 0) ml[t][r] = __ldcg(m_base + off);
+                    if (d == 1) ml[t][r] = __ldcg(l_base + off);
+                }
             }
         }
         if (d < 2) {
 #pragma unroll
-            for (int r = 0; r < kCombinePerLane; ++r) {
-                const int32_t s = j + r * kCombineLanes;
-                if (s < cnt) (d == 0 ? s_m : s_l)[s] = ml[r];
+            for (int t = 0; t < kOwn; ++t) {
+#pragma unroll
+                for (int r = 0; r < kPerSlot; ++r) {
+                    const int32_t s = (j + t * LANES) + r * kCombineSlots;
+                    if (s < cnt) (d == 0 ? s_m : s_l)[s] = ml[t][r];
+                }
             }
         }
         __syncthreads();
@@ -254,21 +263,24 @@ __global__ void __launch_bounds__(kHeadDim * LANES) gqa_decode_combine(const Dec
             const float w = BF16_OUT ? ex2_approx(s_m[i] - m_new) : exp2f(s_m[i] - m_new);
             ltile += s_l[i] * w;
         }
-        float part = 0.f;
 #pragma unroll
-        for (int r = 0; r < kCombinePerLane; ++r) {
-            const int32_t s = j + r * kCombineLanes;
-            if (s < cnt) {
-                const float w = BF16_OUT ? ex2_approx(s_m[s] - m_new) : exp2f(s_m[s] - m_new);
-                part += o[r] * w;
+        for (int t = 0; t < kOwn; ++t) {
+            float part = 0.f;
+#pragma unroll
+            for (int r = 0; r < kPerSlot; ++r) {
+                const int32_t s = (j + t * LANES) + r * kCombineSlots;
+                if (s < cnt) {
+                    const float w = BF16_OUT ? ex2_approx(s_m[s] - m_new) : exp2f(s_m[s] - m_new);
+                    part += o[t][r] * w;
+                }
             }
+            s_part[j + t * LANES][d] = part;
         }
-        s_part[j][d] = part;
         __syncthreads();
         if (j == 0) {
             float tile_acc = s_part[0][d];
 #pragma unroll
-            for (int jj = 1; jj < kCombineLanes; ++jj) tile_acc += s_part[jj][d];
+            for (int v = 1; v < kCombineSlots; ++v) tile_acc += s_part[v][d];
             acc = acc * rescale + tile_acc;
         }
         l_run = l_run * rescale + ltile;
