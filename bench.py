@@ -216,6 +216,8 @@ def run_ours(args) -> None:
         ident = [gqa.ShardComm.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ident, src=0)
         comm = gqa.ShardComm(ident[0], world, rank)
+        if args.gather == "peer":
+            comm.enable_peer_gather(1 << 20)
 
     hq_total, hkv_total, lens, layout_kind, dtype_name = WORKLOADS[args.workload]
     batch = len(lens)
@@ -406,7 +408,7 @@ def run_ours(args) -> None:
                    "l2": f"inputs larger than L2: {slots} cache slot(s) of "
                          f"{slot_bytes / 2**20:.0f} MiB cycled per GPU",
                    "step": "qk-norm+rope+append, split attention, lse combine"
-                           + (", nccl all-gather" if world > 1 else ""),
+                           + (f", {args.gather} all-gather over NVLink" if world > 1 else ""),
                    "split_chunks": plan["split_chunks"], "ctas": plan["num_ctas"],
                    "items": plan["num_items"]},
         "hbm_tbs_aggregate": achieved * world / 1e3,
@@ -437,6 +439,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--workload", choices=tuple(WORKLOADS), default=DEFAULT_WORKLOAD)
+    ap.add_argument("--gather", choices=("peer", "nccl"), default="peer",
+                    help="N > 1: gather the output with peer stores over NVLink or with NCCL")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-graph", action="store_true",
                     help="time eager launches instead of a CUDA-graph replay (profiler runs)")

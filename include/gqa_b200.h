@@ -324,6 +324,24 @@ int32_t gqa_comm_nranks(const gqa_comm* comm);
 /* All-gather of `bytes` bytes per rank on `stream`; recv is [nranks][bytes]. */
 int gqa_comm_all_gather(gqa_comm* comm, const void* send, void* recv, size_t bytes, void* stream);
 
+/*
+ * Collective, once per communicator: sets up the NVLink peer gather for outputs of up to
+ * max_bytes_per_rank bytes per rank. Every rank allocates a window of
+ * 2 * nranks * max_bytes_per_rank bytes that the other ranks map through CUDA IPC (one process
+ * per GPU on one node, all GPUs visible to every process). Afterwards gqa_decode_sharded
+ * gathers with the GPUs' own stores (gqa_comm_peer_gather) whenever the output fits, instead
+ * of ncclAllGather. Synchronises the device. At most 8 ranks.
+ */
+int gqa_comm_enable_peer_gather(gqa_comm* comm, size_t max_bytes_per_rank);
+/*
+ * One gather step with peer stores on `stream`: recv is [nranks][bytes]; bytes is a multiple
+ * of 16 and both buffers are 16-byte aligned. Collective (every rank calls it once per step,
+ * in the same order). A rank whose peers do not arrive within two seconds sets *status_dev to
+ * 2 (when given), leaves recv unspecified and returns: the kernel never hangs.
+ */
+int gqa_comm_peer_gather(gqa_comm* comm, const void* send, void* recv, size_t bytes,
+                         int32_t* status_dev, void* stream);
+
 /* Rank 0 makes the id; the caller hands it to every rank (any host channel). */
 int gqa_comm_unique_id(void* id_out);
 /* Collective over all ranks; the current CUDA device is the rank's GPU. */
@@ -332,8 +350,9 @@ void gqa_comm_destroy(gqa_comm* comm);
 
 /*
  * Runs gqa_decode on this rank's heads (p describes the LOCAL shard: local head counts,
- * local caches) and gathers every rank's output over NVLink with one ncclAllGather on
- * p->stream. p->out is the local output [batch, local_q_heads, head_dim]; gathered is
+ * local caches) and gathers every rank's output over NVLink on p->stream: with the peer-store
+ * kernel when gqa_comm_enable_peer_gather was called and the output fits, else with one
+ * ncclAllGather. p->out is the local output [batch, local_q_heads, head_dim]; gathered is
  * [nranks, batch, local_q_heads, head_dim].
  */
 int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathered);

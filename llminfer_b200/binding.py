@@ -138,6 +138,9 @@ _SIGNATURES = {
     "gqa_shard_plan": (C.c_int, [C.c_int32] * 4 + [C.POINTER(C.c_int32)] * 4),
     "gqa_comm_nranks": (C.c_int32, [C.c_void_p]),
     "gqa_comm_all_gather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "gqa_comm_enable_peer_gather": (C.c_int, [C.c_void_p, C.c_size_t]),
+    "gqa_comm_peer_gather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
+                                       C.c_void_p, C.c_void_p]),
     "gqa_comm_unique_id": (C.c_int, [C.c_void_p]),
     "gqa_comm_init": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
     "gqa_comm_destroy": (None, [C.c_void_p]),
@@ -482,6 +485,27 @@ class ShardComm:
         buf = C.create_string_buffer(COMM_ID_BYTES)
         _check(lib().gqa_comm_unique_id(buf), "gqa_comm_unique_id")
         return buf.raw
+
+    def enable_peer_gather(self, max_bytes_per_rank: int) -> None:
+        """Collective: from now on decode_sharded gathers with peer stores over NVLink."""
+        _check(lib().gqa_comm_enable_peer_gather(self._h, max_bytes_per_rank),
+               "gqa_comm_enable_peer_gather")
+
+    def all_gather(self, send: torch.Tensor, recv: torch.Tensor,
+                   stream: Optional[int] = None) -> None:
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        _check(lib().gqa_comm_all_gather(self._h, _ptr(send), _ptr(recv),
+                                         send.numel() * send.element_size(), stream),
+               "gqa_comm_all_gather")
+
+    def peer_gather(self, send: torch.Tensor, recv: torch.Tensor,
+                    status: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        _check(lib().gqa_comm_peer_gather(self._h, _ptr(send), _ptr(recv),
+                                          send.numel() * send.element_size(), _ptr(status),
+                                          stream), "gqa_comm_peer_gather")
 
     def close(self) -> None:
         if self._h:

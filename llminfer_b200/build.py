@@ -27,7 +27,7 @@ KERNEL_SOURCES = [
     "csrc/session.cu",
     "csrc/static_scratch.cu",
     "csrc/kv_pool.cpp",
-    "csrc/shard_comm.cpp",
+    "csrc/shard_comm.cu",
 ]
 KERNEL_HEADERS = ["csrc/ptx.cuh", "csrc/work_map.cuh", "csrc/decode_kernels.cuh"]
 

@@ -1,0 +1,381 @@
+// KV-head-parallel partition and the gather of the attention output across the GPUs of a node.
+// See include/gqa_b200.h.
+//
+// Two gathers are provided. The plain one is ncclAllGather; NCCL is bound at run time (the
+// copy already loaded in the process if there is one, else libnccl.so.2 from the loader
+// path), so the library has no link-time dependency on it and single-GPU users never load it.
+//
+// The peer gather moves the (small: tens of KiB) outputs with the GPUs' own stores over
+// NVLink. Every rank owns a "window" of device memory that all other ranks map through CUDA
+// IPC: two halves of nranks slots each, plus one arrival flag per half and rank. One kernel
+// per rank and step
+//   1. stores the rank's output into its slot of every rank's window (plain 16-byte stores
+//      to peer memory; no TMA, no multicast),
+//   2. once all its CTAs have stored (ticket counter), publishes the step number in its flag
+//      of every window with a system-scope release,
+//   3. waits, with a time limit, until the flags of all ranks in its own window show the step
+//      number, and copies the window half into the caller's buffer.
+// Steps alternate between the two halves: a rank can run at most one step ahead of the
+// slowest rank (it needs everybody's flag to finish a step), so the half it writes for step
+// e + 1 is never the one a slower rank is still copying out for step e. The step number lives
+// in device memory and is advanced by the kernel itself, so a captured CUDA graph can be
+// replayed. If a wait runs out (a peer died or never called), the kernel sets the caller's
+// status word and the communicator's own, skips the copy and returns: nothing hangs.
+#include "../../include/gqa_b200.h"
+
+#include <cstring>
+#include <dlfcn.h>
+#include <mutex>
+#include <new>
+
+#include <cuda_runtime.h>
+#include <nccl.h>
+
+#include "decode_kernels.cuh"
+#include "ptx.cuh"
+
+namespace {
+
+struct NcclApi {
+    ncclResult_t (*get_unique_id)(ncclUniqueId*);
+    ncclResult_t (*comm_init_rank)(ncclComm_t*, int, ncclUniqueId, int);
+    ncclResult_t (*comm_destroy)(ncclComm_t);
+    ncclResult_t (*all_gather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t,
+                               cudaStream_t);
+    bool ok;
+};
+
+const NcclApi& nccl() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        std::memset(&api, 0, sizeof(api));
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+        if (h == nullptr) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (h == nullptr) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (h == nullptr) return;
+        api.get_unique_id =
+            reinterpret_cast<decltype(api.get_unique_id)>(dlsym(h, "ncclGetUniqueId"));
+        api.comm_init_rank =
+            reinterpret_cast<decltype(api.comm_init_rank)>(dlsym(h, "ncclCommInitRank"));
+        api.comm_destroy = reinterpret_cast<decltype(api.comm_destroy)>(dlsym(h, "ncclCommDestroy"));
+        api.all_gather = reinterpret_cast<decltype(api.all_gather)>(dlsym(h, "ncclAllGather"));
+        api.ok = api.get_unique_id && api.comm_init_rank && api.comm_destroy && api.all_gather;
+    });
+    return api;
+}
+
+}  // namespace
+
+namespace {
+
+constexpr int kMaxPeers = 8;
+constexpr int kGatherCtas = 8;
+constexpr int kGatherThreads = 256;
+constexpr uint64_t kGatherWaitNs = 2000000000ull;
+
+// Control words at the end of a window (all uint32): flags[2][kMaxPeers] arrival flags,
+// then step (completed gathers), ticket_in, ticket_out, status.
+struct WindowCtrl {
+    uint32_t flags[2][kMaxPeers];
+    uint32_t step;
+    uint32_t ticket_in;
+    uint32_t ticket_out;
+    uint32_t status;
+};
+
+struct PeerGatherArgs {
+    uint8_t* windows[kMaxPeers];  // every rank's window as mapped into this process
+    const uint8_t* send;
+    uint8_t* recv;
+    int32_t* status;
+    uint64_t slot_bytes;   // capacity of one slot
+    uint64_t bytes;        // bytes per rank in this step (multiple of 16)
+    int32_t nranks;
+    int32_t rank;
+};
+
+__device__ __forceinline__ WindowCtrl* window_ctrl(uint8_t* window, uint64_t slot_bytes,
+                                                   int nranks) {
+    return reinterpret_cast<WindowCtrl*>(window + 2 * (uint64_t)nranks * slot_bytes);
+}
+
+__device__ __forceinline__ void store_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(kGatherThreads) peer_gather_kernel(const PeerGatherArgs a) {
+    __shared__ uint32_t s_step;
+    __shared__ int s_timed_out;
+    gqa::pdl_launch_dependents();
+    gqa::pdl_wait();  // the attention output and the step counter come from earlier kernels
+    uint8_t* mine = a.windows[a.rank];
+    WindowCtrl* ctrl = window_ctrl(mine, a.slot_bytes, a.nranks);
+    if (threadIdx.x == 0) {
+        s_step = *reinterpret_cast<volatile uint32_t*>(&ctrl->step) + 1;
+        s_timed_out = 0;
+    }
+    __syncthreads();
+    const uint32_t step = s_step;
+    const uint64_t half_off = (uint64_t)(step & 1u) * a.nranks * a.slot_bytes;
+    const uint64_t chunks = a.bytes / 16;
+
+    // 1. my output -> my slot in every rank's window
+    const uint64_t total = chunks * a.nranks;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        const int p = (int)(i / chunks);
+        const uint64_t c = i - (uint64_t)p * chunks;
+        const uint4 v = reinterpret_cast<const uint4*>(a.send)[c];
+        reinterpret_cast<uint4*>(a.windows[p] + half_off + (uint64_t)a.rank * a.slot_bytes)[c] = v;
+    }
+    __syncthreads();
+
+    // 2. the last CTA to get here publishes the step in every window
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const uint32_t ticket = atomicAdd(&ctrl->ticket_in, 1u);
+        if (ticket == gridDim.x - 1) {
+            ctrl->ticket_in = 0;
+            __threadfence_system();
+            for (int p = 0; p < a.nranks; ++p) {
+                WindowCtrl* pc = window_ctrl(a.windows[p], a.slot_bytes, a.nranks);
+                store_release_sys(&pc->flags[step & 1u][a.rank], step);
+            }
+        }
+    }
+
+    // 3. wait for everybody's flag in my window, then copy the half out
+    if (threadIdx.x < a.nranks) {
+        const uint32_t* flag = &ctrl->flags[step & 1u][threadIdx.x];
+        unsigned long long start;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+        while (load_acquire_sys(flag) != step) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (now - start > kGatherWaitNs) {
+                s_timed_out = 1;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (s_timed_out) {
+        if (threadIdx.x == 0) {
+            ctrl->status = 1;
+            if (a.status != nullptr) atomicExch(a.status, 2);
+        }
+    } else {
+        for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+             i += (uint64_t)gridDim.x * blockDim.x) {
+            const int p = (int)(i / chunks);
+            const uint64_t c = i - (uint64_t)p * chunks;
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(
+                                       mine + half_off + (uint64_t)p * a.slot_bytes) + c);
+            reinterpret_cast<uint4*>(a.recv + (uint64_t)p * a.bytes)[c] = v;
+        }
+    }
+    __syncthreads();
+    // The last CTA to finish advances the step counter for the next launch.
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const uint32_t ticket = atomicAdd(&ctrl->ticket_out, 1u);
+        if (ticket == gridDim.x - 1) {
+            ctrl->ticket_out = 0;
+            ctrl->step = step;
+        }
+    }
+}
+
+}  // namespace
+
+struct gqa_comm {
+    ncclComm_t comm;
+    int32_t nranks;
+    int32_t rank;
+    // peer gather (null / zero until gqa_comm_enable_peer_gather)
+    uint8_t* window_local;
+    uint8_t* windows[kMaxPeers];
+    size_t slot_bytes;
+};
+
+extern "C" {
+
+int gqa_shard_plan(int32_t num_q_heads, int32_t num_kv_heads, int32_t nranks, int32_t rank,
+                   int32_t* first_kv_head, int32_t* num_local_kv_heads, int32_t* first_q_head,
+                   int32_t* num_local_q_heads) {
+    if (!first_kv_head || !num_local_kv_heads || !first_q_head || !num_local_q_heads) {
+        return GQA_ERR_NULL;
+    }
+    if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0) {
+        return GQA_ERR_SHAPE;
+    }
+    if (nranks <= 0 || rank < 0 || rank >= nranks) return GQA_ERR_RANGE;
+    if (num_kv_heads % nranks != 0) return GQA_ERR_SHAPE;
+    const int32_t group = num_q_heads / num_kv_heads;
+    const int32_t local = num_kv_heads / nranks;
+    *num_local_kv_heads = local;
+    *first_kv_head = rank * local;
+    *num_local_q_heads = local * group;
+    *first_q_head = rank * local * group;
+    return GQA_OK;
+}
+
+int gqa_comm_unique_id(void* id_out) {
+    if (id_out == nullptr) return GQA_ERR_NULL;
+    static_assert(sizeof(ncclUniqueId) == GQA_COMM_ID_BYTES, "id size");
+    const NcclApi& api = nccl();
+    if (!api.ok) return GQA_ERR_COMM;
+    ncclUniqueId id;
+    if (api.get_unique_id(&id) != ncclSuccess) return GQA_ERR_COMM;
+    std::memcpy(id_out, &id, sizeof(id));
+    return GQA_OK;
+}
+
+int gqa_comm_init(const void* id, int32_t nranks, int32_t rank, gqa_comm** out) {
+    if (id == nullptr || out == nullptr) return GQA_ERR_NULL;
+    *out = nullptr;
+    if (nranks <= 0 || rank < 0 || rank >= nranks) return GQA_ERR_RANGE;
+    const NcclApi& api = nccl();
+    if (!api.ok) return GQA_ERR_COMM;
+    gqa_comm* c = new (std::nothrow) gqa_comm();
+    if (c == nullptr) return GQA_ERR_COMM;
+    ncclUniqueId uid;
+    std::memcpy(&uid, id, sizeof(uid));
+    if (api.comm_init_rank(&c->comm, nranks, uid, rank) != ncclSuccess) {
+        delete c;
+        return GQA_ERR_COMM;
+    }
+    c->nranks = nranks;
+    c->rank = rank;
+    c->window_local = nullptr;
+    c->slot_bytes = 0;
+    for (int p = 0; p < kMaxPeers; ++p) c->windows[p] = nullptr;
+    *out = c;
+    return GQA_OK;
+}
+
+int gqa_comm_enable_peer_gather(gqa_comm* comm, size_t max_bytes_per_rank) {
+    if (comm == nullptr) return GQA_ERR_NULL;
+    if (comm->window_local != nullptr) return GQA_OK;
+    if (comm->nranks > kMaxPeers || max_bytes_per_rank == 0) return GQA_ERR_SHAPE;
+    const NcclApi& api = nccl();
+    if (!api.ok) return GQA_ERR_COMM;
+    const size_t slot = (max_bytes_per_rank + 255) / 256 * 256;
+    const size_t window_bytes = 2 * (size_t)comm->nranks * slot + sizeof(WindowCtrl);
+    uint8_t* local = nullptr;
+    cudaIpcMemHandle_t* d_handles = nullptr;
+    cudaIpcMemHandle_t handles[kMaxPeers];
+    bool ok = cudaMalloc(&local, window_bytes) == cudaSuccess &&
+              cudaMemset(local, 0, window_bytes) == cudaSuccess &&
+              cudaDeviceSynchronize() == cudaSuccess &&
+              cudaIpcGetMemHandle(&handles[comm->rank], local) == cudaSuccess &&
+              cudaMalloc(&d_handles, sizeof(cudaIpcMemHandle_t) * kMaxPeers) == cudaSuccess &&
+              cudaMemcpy(d_handles + comm->rank, &handles[comm->rank], sizeof(cudaIpcMemHandle_t),
+                         cudaMemcpyHostToDevice) == cudaSuccess;
+    // Every rank learns every window's handle through one small all-gather.
+    ok = ok && api.all_gather(d_handles + comm->rank, d_handles, sizeof(cudaIpcMemHandle_t),
+                              ncclInt8, comm->comm, nullptr) == ncclSuccess &&
+         cudaDeviceSynchronize() == cudaSuccess &&
+         cudaMemcpy(handles, d_handles, sizeof(cudaIpcMemHandle_t) * comm->nranks,
+                    cudaMemcpyDeviceToHost) == cudaSuccess;
+    if (d_handles != nullptr) cudaFree(d_handles);
+    if (!ok) {
+        if (local != nullptr) cudaFree(local);
+        return GQA_ERR_COMM;
+    }
+    for (int p = 0; p < comm->nranks; ++p) {
+        if (p == comm->rank) {
+            comm->windows[p] = local;
+            continue;
+        }
+        void* mapped = nullptr;
+        if (cudaIpcOpenMemHandle(&mapped, handles[p], cudaIpcMemLazyEnablePeerAccess) !=
+            cudaSuccess) {
+            for (int q = 0; q < p; ++q) {
+                if (q != comm->rank && comm->windows[q]) cudaIpcCloseMemHandle(comm->windows[q]);
+                comm->windows[q] = nullptr;
+            }
+            cudaFree(local);
+            return GQA_ERR_COMM;
+        }
+        comm->windows[p] = static_cast<uint8_t*>(mapped);
+    }
+    comm->window_local = local;
+    comm->slot_bytes = slot;
+    return GQA_OK;
+}
+
+int gqa_comm_peer_gather(gqa_comm* comm, const void* send, void* recv, size_t bytes,
+                         int32_t* status_dev, void* stream) {
+    if (comm == nullptr || send == nullptr || recv == nullptr) return GQA_ERR_NULL;
+    if (comm->window_local == nullptr) return GQA_ERR_COMM;
+    if (bytes == 0 || bytes % 16 != 0 || bytes > comm->slot_bytes) return GQA_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(send) | reinterpret_cast<uintptr_t>(recv)) & 15u) {
+        return GQA_ERR_ALIGN;
+    }
+    PeerGatherArgs a;
+    std::memset(&a, 0, sizeof(a));
+    for (int p = 0; p < comm->nranks; ++p) a.windows[p] = comm->windows[p];
+    a.send = static_cast<const uint8_t*>(send);
+    a.recv = static_cast<uint8_t*>(recv);
+    a.status = status_dev;
+    a.slot_bytes = comm->slot_bytes;
+    a.bytes = bytes;
+    a.nranks = comm->nranks;
+    a.rank = comm->rank;
+    const cudaError_t e = gqa::launch_pdl(peer_gather_kernel, dim3(kGatherCtas),
+                                          dim3(kGatherThreads), 0,
+                                          reinterpret_cast<cudaStream_t>(stream), a);
+    return e == cudaSuccess ? GQA_OK : GQA_ERR_CUDA;
+}
+
+void gqa_comm_destroy(gqa_comm* comm) {
+    if (comm == nullptr) return;
+    if (comm->window_local != nullptr) {
+        cudaDeviceSynchronize();
+        for (int p = 0; p < comm->nranks; ++p) {
+            if (p != comm->rank && comm->windows[p] != nullptr) {
+                cudaIpcCloseMemHandle(comm->windows[p]);
+            }
+        }
+        cudaFree(comm->window_local);
+        comm->window_local = nullptr;
+    }
+    const NcclApi& api = nccl();
+    if (api.ok && comm->comm != nullptr) api.comm_destroy(comm->comm);
+    delete comm;
+}
+
+int32_t gqa_comm_nranks(const gqa_comm* comm) { return comm == nullptr ? 0 : comm->nranks; }
+
+int gqa_comm_all_gather(gqa_comm* comm, const void* send, void* recv, size_t bytes, void* stream) {
+    if (comm == nullptr || send == nullptr || recv == nullptr) return GQA_ERR_NULL;
+    const NcclApi& api = nccl();
+    if (!api.ok) return GQA_ERR_COMM;
+    if (api.all_gather(send, recv, bytes, ncclInt8, comm->comm,
+                       reinterpret_cast<cudaStream_t>(stream)) != ncclSuccess) {
+        return GQA_ERR_COMM;
+    }
+    return GQA_OK;
+}
+
+int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathered) {
+    if (p == nullptr || comm == nullptr || gathered == nullptr) return GQA_ERR_NULL;
+    const int rc = gqa_decode(p);
+    if (rc != GQA_OK) return rc;
+    const size_t elem = p->dtype == GQA_DTYPE_F32 ? 4 : 2;
+    const size_t bytes = (size_t)p->batch * p->num_q_heads * p->head_dim * elem;
+    if (comm->window_local != nullptr && bytes <= comm->slot_bytes) {
+        return gqa_comm_peer_gather(comm, p->out, gathered, bytes, p->status_dev, p->stream);
+    }
+    return gqa_comm_all_gather(comm, p->out, gathered, bytes, p->stream);
+}
+
+}  // extern "C"

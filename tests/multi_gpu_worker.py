@@ -72,6 +72,37 @@ def main() -> None:
     abs_err, rel_err = H.errors(whole.float().cpu().numpy(), want)
     assert abs_err <= 2e-2 and rel_err <= 1e-2, (abs_err, rel_err)
 
+    # The same through the NVLink peer-store gather, step after step (the two window halves
+    # alternate) and inside a replayed CUDA graph (the step counter lives on the device).
+    comm.enable_peer_gather(batch * per_q * d * 2)
+    for _ in range(5):
+        again = run(q_l, k_l, v_l, per_q, per_kv, sharded=True)
+        assert torch.equal(again.view(torch.int16), full.view(torch.int16)), "peer gather != unsharded"
+    send = torch.zeros(1024, dtype=torch.int32, device=dev)
+    recv = torch.zeros(world, 1024, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    seen = torch.zeros(6, world, dtype=torch.int32, device=dev)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        comm.peer_gather(send, recv, status)  # warm-up outside the capture
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(3):
+                send.add_(rank + 1)
+                comm.peer_gather(send, recv, status)
+                seen[i].copy_(recv[:, 7])
+        for rep in range(2):
+            graph.replay()
+            torch.cuda.synchronize()
+            base = 3 * rep
+            for i in range(3):
+                want = [(base + i + 1) * (r + 1) for r in range(world)]
+                assert seen[i].tolist() == want, (rep, i, seen[i].tolist(), want)
+    torch.cuda.current_stream().wait_stream(side)
+    assert int(status.item()) == 0
+
     # The host-buffer step with the gather inside.
     layout_l = gqa.layout_pool(num_blocks, block_tokens, per_kv)
     session = gqa.Session(batch, per_q, per_kv, blocks_per_seq * block_tokens)
