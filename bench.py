@@ -370,6 +370,9 @@ def run_ours(args) -> None:
             print(json.dumps({"attention_only_us_per_layer": attn_us, "us_per_layer": us_per_layer,
                               "roofline": {"achieved": achieved, "frac": achieved / peak},
                               "plan": plan}))
+        if comm is not None:
+            comm.close()
+            dist.destroy_process_group()
         return
     if not has_front:
         raise SystemExit("the end-to-end leg needs the BF16 front stage; use --attn-only")

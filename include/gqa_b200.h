@@ -327,7 +327,7 @@ int gqa_comm_all_gather(gqa_comm* comm, const void* send, void* recv, size_t byt
 /*
  * Collective, once per communicator: sets up the NVLink peer gather for outputs of up to
  * max_bytes_per_rank bytes per rank. Every rank allocates a window of
- * 2 * nranks * max_bytes_per_rank bytes that the other ranks map through CUDA IPC (one process
+ * 4 * nranks * max_bytes_per_rank bytes that the other ranks map through CUDA IPC (one process
  * per GPU on one node, all GPUs visible to every process). Afterwards gqa_decode_sharded
  * gathers with the GPUs' own stores (gqa_comm_peer_gather) whenever the output fits, instead
  * of ncclAllGather. Synchronises the device. At most 8 ranks.

@@ -7,20 +7,20 @@
 //
 // The peer gather moves the (small: tens of KiB) outputs with the GPUs' own stores over
 // NVLink. Every rank owns a "window" of device memory that all other ranks map through CUDA
-// IPC: two halves of nranks slots each, plus one arrival flag per half and rank. One kernel
-// per rank and step
-//   1. stores the rank's output into its slot of every rank's window (plain 16-byte stores
-//      to peer memory; no TMA, no multicast),
-//   2. once all its CTAs have stored (ticket counter), publishes the step number in its flag
-//      of every window with a system-scope release,
-//   3. waits, with a time limit, until the flags of all ranks in its own window show the step
-//      number, and copies the window half into the caller's buffer.
+// IPC: two halves of nranks slots each. Data travels as 8-byte words that carry 4 bytes of
+// payload and the 4-byte step number (8-byte stores are single transactions, so a word is
+// seen either whole or not at all): no fences and no separate flags are needed, a word whose
+// upper half shows the current step has arrived. One kernel per rank and step
+//   1. stores the rank's output, word by word, into its slot of every rank's window (plain
+//      stores to peer memory; no TMA, no multicast),
+//   2. polls, with a time limit, the slots of all ranks in its own window until every word
+//      shows the step number, and writes the payloads to the caller's buffer.
 // Steps alternate between the two halves: a rank can run at most one step ahead of the
-// slowest rank (it needs everybody's flag to finish a step), so the half it writes for step
-// e + 1 is never the one a slower rank is still copying out for step e. The step number lives
+// slowest rank (it needs everybody's words to finish a step), so the half it writes for step
+// e + 1 is never the one a slower rank is still reading for step e. The step number lives
 // in device memory and is advanced by the kernel itself, so a captured CUDA graph can be
 // replayed. If a wait runs out (a peer died or never called), the kernel sets the caller's
-// status word and the communicator's own, skips the copy and returns: nothing hangs.
+// status word and the window's own, and returns: nothing hangs.
 #include "../../include/gqa_b200.h"
 
 #include <cstring>
@@ -70,27 +70,25 @@ const NcclApi& nccl() {
 namespace {
 
 constexpr int kMaxPeers = 8;
-constexpr int kGatherCtas = 8;
+constexpr int kGatherCtas = 16;
 constexpr int kGatherThreads = 256;
 constexpr uint64_t kGatherWaitNs = 2000000000ull;
 
-// Control words at the end of a window (all uint32): flags[2][kMaxPeers] arrival flags,
-// then step (completed gathers), ticket_in, ticket_out, status.
+// Control words at the end of a window.
 struct WindowCtrl {
-    uint32_t flags[2][kMaxPeers];
-    uint32_t step;
-    uint32_t ticket_in;
-    uint32_t ticket_out;
-    uint32_t status;
+    uint32_t step;        // completed gathers
+    uint32_t ticket_out;  // CTAs that finished the current gather
+    uint32_t status;      // 1 after a wait ran out
+    uint32_t pad;
 };
 
 struct PeerGatherArgs {
     uint8_t* windows[kMaxPeers];  // every rank's window as mapped into this process
-    const uint8_t* send;
-    uint8_t* recv;
+    const uint32_t* send;
+    uint32_t* recv;
     int32_t* status;
-    uint64_t slot_bytes;   // capacity of one slot
-    uint64_t bytes;        // bytes per rank in this step (multiple of 16)
+    uint64_t slot_bytes;   // capacity of one slot (payload + step words)
+    uint64_t words;        // 4-byte payload words per rank in this step
     int32_t nranks;
     int32_t rank;
 };
@@ -98,16 +96,6 @@ struct PeerGatherArgs {
 __device__ __forceinline__ WindowCtrl* window_ctrl(uint8_t* window, uint64_t slot_bytes,
                                                    int nranks) {
     return reinterpret_cast<WindowCtrl*>(window + 2 * (uint64_t)nranks * slot_bytes);
-}
-
-__device__ __forceinline__ void store_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
 }
 
 __global__ void __launch_bounds__(kGatherThreads) peer_gather_kernel(const PeerGatherArgs a) {
@@ -124,66 +112,50 @@ __global__ void __launch_bounds__(kGatherThreads) peer_gather_kernel(const PeerG
     __syncthreads();
     const uint32_t step = s_step;
     const uint64_t half_off = (uint64_t)(step & 1u) * a.nranks * a.slot_bytes;
-    const uint64_t chunks = a.bytes / 16;
+    const uint64_t total = a.words * a.nranks;
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t nthreads = (uint64_t)gridDim.x * blockDim.x;
 
-    // 1. my output -> my slot in every rank's window
-    const uint64_t total = chunks * a.nranks;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (uint64_t)gridDim.x * blockDim.x) {
-        const int p = (int)(i / chunks);
-        const uint64_t c = i - (uint64_t)p * chunks;
-        const uint4 v = reinterpret_cast<const uint4*>(a.send)[c];
-        reinterpret_cast<uint4*>(a.windows[p] + half_off + (uint64_t)a.rank * a.slot_bytes)[c] = v;
-    }
-    __syncthreads();
-
-    // 2. the last CTA to get here publishes the step in every window
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        const uint32_t ticket = atomicAdd(&ctrl->ticket_in, 1u);
-        if (ticket == gridDim.x - 1) {
-            ctrl->ticket_in = 0;
-            __threadfence_system();
-            for (int p = 0; p < a.nranks; ++p) {
-                WindowCtrl* pc = window_ctrl(a.windows[p], a.slot_bytes, a.nranks);
-                store_release_sys(&pc->flags[step & 1u][a.rank], step);
-            }
-        }
+    // 1. my output -> my slot in every rank's window, each word tagged with the step
+    for (uint64_t i = tid; i < total; i += nthreads) {
+        const int p = (int)(i / a.words);
+        const uint64_t w = i - (uint64_t)p * a.words;
+        const unsigned long long word = ((unsigned long long)step << 32) | a.send[w];
+        unsigned long long* dst = reinterpret_cast<unsigned long long*>(
+            a.windows[p] + half_off + (uint64_t)a.rank * a.slot_bytes) + w;
+        asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(dst), "l"(word) : "memory");
     }
 
-    // 3. wait for everybody's flag in my window, then copy the half out
-    if (threadIdx.x < a.nranks) {
-        const uint32_t* flag = &ctrl->flags[step & 1u][threadIdx.x];
-        unsigned long long start;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
-        while (load_acquire_sys(flag) != step) {
+    // 2. every word of every rank's slot in my window, as soon as it shows this step
+    unsigned long long start;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+    bool timed_out = false;
+    for (uint64_t i = tid; i < total && !timed_out; i += nthreads) {
+        const int p = (int)(i / a.words);
+        const uint64_t w = i - (uint64_t)p * a.words;
+        const unsigned long long* src = reinterpret_cast<const unsigned long long*>(
+            mine + half_off + (uint64_t)p * a.slot_bytes) + w;
+        unsigned long long word;
+        while (true) {
+            asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word) : "l"(src) : "memory");
+            if ((uint32_t)(word >> 32) == step) break;
             unsigned long long now;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
             if (now - start > kGatherWaitNs) {
-                s_timed_out = 1;
+                timed_out = true;
                 break;
             }
         }
+        if (!timed_out) a.recv[(uint64_t)p * a.words + w] = (uint32_t)word;
     }
+    if (timed_out) s_timed_out = 1;
     __syncthreads();
-    if (s_timed_out) {
-        if (threadIdx.x == 0) {
+    if (threadIdx.x == 0) {
+        if (s_timed_out) {
             ctrl->status = 1;
             if (a.status != nullptr) atomicExch(a.status, 2);
         }
-    } else {
-        for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-             i += (uint64_t)gridDim.x * blockDim.x) {
-            const int p = (int)(i / chunks);
-            const uint64_t c = i - (uint64_t)p * chunks;
-            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(
-                                       mine + half_off + (uint64_t)p * a.slot_bytes) + c);
-            reinterpret_cast<uint4*>(a.recv + (uint64_t)p * a.bytes)[c] = v;
-        }
-    }
-    __syncthreads();
-    // The last CTA to finish advances the step counter for the next launch.
-    if (threadIdx.x == 0) {
+        // The last CTA to finish advances the step counter for the next launch.
         __threadfence();
         const uint32_t ticket = atomicAdd(&ctrl->ticket_out, 1u);
         if (ticket == gridDim.x - 1) {
@@ -267,7 +239,8 @@ int gqa_comm_enable_peer_gather(gqa_comm* comm, size_t max_bytes_per_rank) {
     if (comm->nranks > kMaxPeers || max_bytes_per_rank == 0) return GQA_ERR_SHAPE;
     const NcclApi& api = nccl();
     if (!api.ok) return GQA_ERR_COMM;
-    const size_t slot = (max_bytes_per_rank + 255) / 256 * 256;
+    // A slot holds the payload twice over: every 4 payload bytes travel with a 4-byte step tag.
+    const size_t slot = (2 * max_bytes_per_rank + 255) / 256 * 256;
     const size_t window_bytes = 2 * (size_t)comm->nranks * slot + sizeof(WindowCtrl);
     uint8_t* local = nullptr;
     cudaIpcMemHandle_t* d_handles = nullptr;
@@ -316,18 +289,18 @@ int gqa_comm_peer_gather(gqa_comm* comm, const void* send, void* recv, size_t by
                          int32_t* status_dev, void* stream) {
     if (comm == nullptr || send == nullptr || recv == nullptr) return GQA_ERR_NULL;
     if (comm->window_local == nullptr) return GQA_ERR_COMM;
-    if (bytes == 0 || bytes % 16 != 0 || bytes > comm->slot_bytes) return GQA_ERR_SHAPE;
+    if (bytes == 0 || bytes % 16 != 0 || 2 * bytes > comm->slot_bytes) return GQA_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(send) | reinterpret_cast<uintptr_t>(recv)) & 15u) {
         return GQA_ERR_ALIGN;
     }
     PeerGatherArgs a;
     std::memset(&a, 0, sizeof(a));
     for (int p = 0; p < comm->nranks; ++p) a.windows[p] = comm->windows[p];
-    a.send = static_cast<const uint8_t*>(send);
-    a.recv = static_cast<uint8_t*>(recv);
+    a.send = static_cast<const uint32_t*>(send);
+    a.recv = static_cast<uint32_t*>(recv);
     a.status = status_dev;
     a.slot_bytes = comm->slot_bytes;
-    a.bytes = bytes;
+    a.words = bytes / 4;
     a.nranks = comm->nranks;
     a.rank = comm->rank;
     const cudaError_t e = gqa::launch_pdl(peer_gather_kernel, dim3(kGatherCtas),
@@ -372,7 +345,7 @@ int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathere
     if (rc != GQA_OK) return rc;
     const size_t elem = p->dtype == GQA_DTYPE_F32 ? 4 : 2;
     const size_t bytes = (size_t)p->batch * p->num_q_heads * p->head_dim * elem;
-    if (comm->window_local != nullptr && bytes <= comm->slot_bytes) {
+    if (comm->window_local != nullptr && 2 * bytes <= comm->slot_bytes && bytes % 16 == 0) {
         return gqa_comm_peer_gather(comm, p->out, gathered, bytes, p->status_dev, p->stream);
     }
     return gqa_comm_all_gather(comm, p->out, gathered, bytes, p->stream);
