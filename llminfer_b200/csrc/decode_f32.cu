@@ -188,8 +188,9 @@ constexpr int kCombineSlots = 8;   // partial sums per channel per pass, whateve
 // pass are dealt to 8 slots (split s goes to slot s % 8); a thread owns 8 / LANES slots and
 // adds each slot's splits in ascending order, then the slots are added in ascending order.
 // The result therefore does not depend on LANES, which is only a matter of how many threads
-// share the loads: 8 lanes (1024 threads) for small grids, 2 for grids that would not fit the
-// GPU in one wave at that size. Every load of a pass (O rows, m and l) is issued before any
+// share the loads: 4 lanes (512 threads, few enough registers to sit on an SM next to a CTA of
+// the streaming kernel, so that neither kernel delays the other's early launch) for small
+// grids, 2 for grids that would not fit the GPU in one wave at that size. Every load of a pass (O rows, m and l) is issued before any
 // is used, so a pass costs one trip to L2; longer split lists fold pass by pass with a running
 // (M, L). Partial records are read with L1-bypassing loads: the kernel that wrote them may
 // still have been running when this one started.
@@ -315,12 +316,12 @@ cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t s
     const int grid = args.batch * args.num_q_heads;
     const bool wide = grid <= 160;
     if (bf16_out) {
-        return wide ? launch_pdl(gqa_decode_combine<true, 8>, dim3(grid), dim3(kHeadDim * 8), smem,
+        return wide ? launch_pdl(gqa_decode_combine<true, 4>, dim3(grid), dim3(kHeadDim * 4), smem,
                                  stream, args)
                     : launch_pdl(gqa_decode_combine<true, 2>, dim3(grid), dim3(kHeadDim * 2), smem,
                                  stream, args);
     }
-    return wide ? launch_pdl(gqa_decode_combine<false, 8>, dim3(grid), dim3(kHeadDim * 8), smem,
+    return wide ? launch_pdl(gqa_decode_combine<false, 4>, dim3(grid), dim3(kHeadDim * 4), smem,
                              stream, args)
                 : launch_pdl(gqa_decode_combine<false, 2>, dim3(grid), dim3(kHeadDim * 2), smem,
                              stream, args);
