@@ -467,14 +467,8 @@ cudaError_t launch_stream_bf16(const StreamShape& shape, const CUtensorMap& tk,
     GQA_VARIANT(4, 1, 64, 1)
     GQA_VARIANT(4, 2, 32, 1)
     GQA_VARIANT(4, 3, 32, 1)
-    GQA_VARIANT(5, 1, 64, 1)
-    GQA_VARIANT(3, 2, 64, 1)
     GQA_VARIANT(8, 1, 32, 1)
     GQA_VARIANT(4, 1, 32, 2)
-    GQA_VARIANT(2, 1, 64, 2)
-    GQA_VARIANT(2, 2, 32, 2)
-    GQA_VARIANT(4, 1, 16, 3)
-    GQA_VARIANT(2, 1, 32, 3)
 #undef GQA_VARIANT
     return cudaErrorInvalidValue;
 }

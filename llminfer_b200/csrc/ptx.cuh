@@ -41,17 +41,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
-// Bounded wait: gives up after `max_tries` failed polls and reports false. try_wait itself
-// blocks for a hardware-defined slice, so the budget is many milliseconds, far beyond any
-// healthy copy, yet the kernel can never spin forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  uint32_t max_tries) {
-    for (uint32_t i = 0; i < max_tries; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-    }
-    return false;
-}
-
 // Orders earlier generic-proxy accesses to shared memory before later async-proxy ones.
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

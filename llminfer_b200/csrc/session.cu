@@ -1,7 +1,14 @@
-// One decode step driven from host buffers: stage the new token's rows on the device, run
-// the front stage and the attention, bring the output back. See include/gqa_b200.h.
+// One decode step driven from host buffers. See include/gqa_b200.h.
+//
+// The new token's rows are small (tens of KiB), so no copy engine is involved: the caller's
+// rows are placed in a pinned, device-mapped block that the front-stage kernel reads over the
+// bus directly (it writes the rotated query to device memory, where the attention kernel reads
+// it many times), and the attention (or the gather) writes its output straight into a second
+// pinned block. The step then waits for the stream and hands the output to the caller.
+// GQA_SESSION_COPIES=1 in the environment selects explicit cudaMemcpyAsync staging instead.
 #include "../../include/gqa_b200.h"
 
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -28,6 +35,7 @@ struct gqa_session {
     size_t workspace_bytes;
     float* sin_table;  // [max_seq_len, head_dim / 2], built once at creation
     float* cos_table;
+    bool zero_copy;    // kernels read / write the pinned blocks directly
 };
 
 namespace {
@@ -77,6 +85,8 @@ int gqa_session_create(int32_t dtype, int32_t max_batch, int32_t num_q_heads,
     s->num_kv_heads = num_kv_heads;
     s->head_dim = head_dim;
     s->max_seq_len = max_seq_len;
+    const char* copies = std::getenv("GQA_SESSION_COPIES");
+    s->zero_copy = !(copies != nullptr && copies[0] == '1');
     s->in_bytes = q_bytes(s, max_batch) + 2 * kv_bytes(s, max_batch) + 2 * (size_t)max_batch * 4;
     int sms = 0, dev = 0;
     bool ok = cudaGetDevice(&dev) == cudaSuccess &&
@@ -136,10 +146,15 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
         lens[b] = positions_host[b] + 1;
     }
     const size_t used = off_pos + (size_t)batch * 4;
-    if (cudaMemcpyAsync(s->dev_in, s->host_in, used, cudaMemcpyHostToDevice, s->stream) !=
-        cudaSuccess) {
+    // Pinned memory is mapped into the device's address space at the same address.
+    const uint8_t* in = s->zero_copy ? s->host_in : s->dev_in;
+    if (!s->zero_copy &&
+        cudaMemcpyAsync(s->dev_in, s->host_in, used, cudaMemcpyHostToDevice, s->stream) !=
+            cudaSuccess) {
         return GQA_ERR_CUDA;
     }
+    bool uniform = true;
+    for (int32_t b = 1; b < batch; ++b) uniform = uniform && positions_host[b] == positions_host[0];
 
     gqa_front_params f;
     std::memset(&f, 0, sizeof(f));
@@ -151,10 +166,10 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     f.fixed_block = fixed_block;
     f.eps = 1e-6f;
     f.layout = *layout;
-    f.q = s->dev_in;
+    f.q = in;
     f.q_out = s->dev_in;
-    f.k_new = s->dev_in + off_k;
-    f.v_new = s->dev_in + off_v;
+    f.k_new = in + off_k;
+    f.v_new = in + off_v;
     f.qk_weight = qk_weight_dev;
     f.sin_cache = s->sin_table;
     f.cos_cache = s->cos_table;
@@ -162,7 +177,8 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     f.k_cache = k_cache;
     f.v_cache = v_cache;
     f.positions_host = poss;
-    f.positions_dev = reinterpret_cast<const int32_t*>(s->dev_in + off_pos);
+    // Equal positions travel by value; otherwise the kernels read them from the staged block.
+    f.positions_dev = uniform ? nullptr : reinterpret_cast<const int32_t*>(in + off_pos);
     f.block_table_dev = block_table_dev;
     f.stream = s->stream;
     int rc = gqa_qk_norm_rope_append(&f);
@@ -181,15 +197,16 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     p.q = s->dev_in;
     p.k_cache = k_cache;
     p.v_cache = v_cache;
-    p.out = s->dev_out;
+    const bool out_to_host = s->zero_copy && comm == nullptr;
+    p.out = out_to_host ? s->host_out : s->dev_out;
     p.workspace = s->workspace;
     p.workspace_bytes = s->workspace_bytes;
     p.seq_lens_host = lens;
-    p.seq_lens_dev = reinterpret_cast<const int32_t*>(s->dev_in + off_len);
+    p.seq_lens_dev = uniform ? nullptr : reinterpret_cast<const int32_t*>(in + off_len);
     p.block_table_dev = block_table_dev;
     p.stream = s->stream;
-    // Ahead of the attention in this stream are the H2D copy of the new rows and the front
-    // stage, which writes the cache rows of the new positions only.
+    // Ahead of the attention in this stream is the front stage, which writes the cache rows
+    // of the new positions only.
     p.early_prefetch = 1;
     rc = gqa_decode(&p);
     if (rc != GQA_OK) return rc;
@@ -210,21 +227,30 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
             }
             s->gather_bytes = cap;
         }
-        rc = gqa_comm_all_gather(comm, s->dev_out, s->dev_gather, qb, s->stream);
-        if (rc != GQA_OK) return rc;
-        if (cudaMemcpyAsync(s->host_gather, s->dev_gather, total, cudaMemcpyDeviceToHost,
-                            s->stream) != cudaSuccess ||
-            cudaStreamSynchronize(s->stream) != cudaSuccess) {
-            return GQA_ERR_CUDA;
+        // The peer-store gather can deliver into the pinned block itself; NCCL gathers on the
+        // device and a copy follows.
+        bool on_host = false;
+        if (s->zero_copy) {
+            rc = gqa_comm_peer_gather(comm, s->dev_out, s->host_gather, qb, nullptr, s->stream);
+            on_host = rc == GQA_OK;
         }
+        if (!on_host) {
+            rc = gqa_comm_all_gather(comm, s->dev_out, s->dev_gather, qb, s->stream);
+            if (rc != GQA_OK) return rc;
+            if (cudaMemcpyAsync(s->host_gather, s->dev_gather, total, cudaMemcpyDeviceToHost,
+                                s->stream) != cudaSuccess) {
+                return GQA_ERR_CUDA;
+            }
+        }
+        if (cudaStreamSynchronize(s->stream) != cudaSuccess) return GQA_ERR_CUDA;
         std::memcpy(out_host, s->host_gather, total);
         return GQA_OK;
     }
-    if (cudaMemcpyAsync(s->host_out, s->dev_out, qb, cudaMemcpyDeviceToHost, s->stream) !=
-            cudaSuccess ||
-        cudaStreamSynchronize(s->stream) != cudaSuccess) {
+    if (!out_to_host && cudaMemcpyAsync(s->host_out, s->dev_out, qb, cudaMemcpyDeviceToHost,
+                                        s->stream) != cudaSuccess) {
         return GQA_ERR_CUDA;
     }
+    if (cudaStreamSynchronize(s->stream) != cudaSuccess) return GQA_ERR_CUDA;
     std::memcpy(out_host, s->host_out, qb);
     return GQA_OK;
 }
