@@ -62,61 +62,99 @@ def algorithmic_bytes(hq: int, hkv: int, lens, elem: int = 2) -> int:
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clock and throttle reasons of one GPU while a region runs.
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    Reads through NVML (read-only queries, about every millisecond, so that even a timed
+    region of a few milliseconds is covered); falls back to polling nvidia-smi.
+    """
+
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40),
+               ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, index: int):
         self.index = index
-        self.rows = []
-        self.proc = None
-        self.thread = None
+        self.clocks = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _nvml_loop(self, nvml, handle):
+        while not self._stop.is_set():
+            try:
+                self.clocks.append(float(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)))
+                mask = nvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                for name, bit in self.REASONS:
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                break
+            time.sleep(0.001)
+
+    def _smi_loop(self):
+        fields = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+                  "clocks_event_reasons.hw_thermal_slowdown,"
+                  "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={fields}",
+                 "--format=csv,noheader,nounits", "-lms", "20"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        names = [n for n, _ in self.REASONS]
+        while not self._stop.is_set():
+            line = proc.stdout.readline()
+            if not line:
+                break
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                self.clocks.append(float(parts[0]))
+                self.max_mhz = float(parts[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:]):
+                if flag.lower().startswith("active"):
+                    self.reasons.add(name)
+        proc.terminate()
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml as nvml
+            nvml.nvmlInit()
+            # NVML counts physical GPUs; honour CUDA_VISIBLE_DEVICES when it lists indices.
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            ids = [v for v in visible.split(",") if v.strip().isdigit()]
+            physical = int(ids[self.index]) if self.index < len(ids) else self.index
+            handle = nvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_mhz = float(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM))
+            self._thread = threading.Thread(target=self._nvml_loop, args=(nvml, handle), daemon=True)
+        except Exception:
+            self._thread = threading.Thread(target=self._smi_loop, daemon=True)
+        self._thread.start()
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) == 6:
-                self.rows.append(parts)
-
     def __exit__(self, *exc):
-        if self.proc is not None:
-            time.sleep(0.15)
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=2)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=3)
 
     def summary(self) -> dict:
-        clocks, reasons, mx = [], set(), None
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for row in self.rows:
-            try:
-                clocks.append(float(row[0]))
-                mx = float(row[1])
-            except ValueError:
-                continue
-            for name, flag in zip(names, row[2:]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        clocks.sort()
-        med = clocks[len(clocks) // 2] if clocks else None
-        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons),
+        clocks = sorted(self.clocks)
+        # The clock under load: idle samples before and after the region sit at the low end.
+        busy = clocks[len(clocks) // 2:] if clocks else []
+        med = busy[len(busy) // 2] if busy else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
                 "samples": len(clocks)}
+
+
+# DRAM traffic per algorithmic byte of the streaming kernel, from one ncu capture
+# (profiles/ncu_full_gqa_decode_stream_bf16_b1_ctx131072.md: 536.94 MB read + 3.83 MB written
+# for 536.90 MB algorithmic). Traffic grows in proportion to the keys processed, so the
+# capture of the batch-1 case is scaled by the algorithmic bytes of the workload timed here.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = (536.942336 + 3.828480) / 536.903680
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -387,12 +425,16 @@ def run_ours(args) -> None:
     for i in range(warmup):
         e2e_step(i)
     barrier()
-    t0 = time.perf_counter()
-    for i in range(steps):
-        e2e_step(i)
-    barrier()
-    e2e_us = max_over_ranks((time.perf_counter() - t0) * 1e3) * 1e3 / steps
+    with ClockSampler(local_rank) as e2e_clocks:
+        t0 = time.perf_counter()
+        for i in range(steps):
+            e2e_step(i)
+        barrier()
+        e2e_us = max_over_ranks((time.perf_counter() - t0) * 1e3) * 1e3 / steps
     session.close()
+    e2e_clock_info = e2e_clocks.summary()
+    clock_info["reasons"] = sorted(set(clock_info["reasons"]) | set(e2e_clock_info["reasons"]))
+    clock_info["samples_e2e"] = e2e_clock_info["samples"]
     h2d = (hq + 2 * hkv) * HEAD_DIM * 2 * batch + 8 * batch
     d2h = out_host.numel() * 2
 
@@ -419,7 +461,9 @@ def run_ours(args) -> None:
         "roofline": {"bound": "hbm", "kernel": "gqa_decode_stream_bf16 (+ lse combine)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": peak_kind, "frac_of_8tbs_nominal": achieved / 8000.0,
-                     "algorithmic_bytes_per_launch": rank_bytes, "traffic": None},
+                     "algorithmic_bytes_per_launch": rank_bytes,
+                     "traffic": int(rank_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE),
+                     "traffic_source": "ncu capture of the batch-1 case, scaled by bytes"},
         "e2e": {"value": e2e_us, "unit": "us/layer", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": 3 * steps,
