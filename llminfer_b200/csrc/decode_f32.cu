@@ -88,22 +88,28 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
             const int32_t t0 = k * kChunkKeys;
             const int32_t valid = min(kChunkKeys, it.len - t0);
 
-            // Scores: lane j ends up holding the G scores of key t0 + j.
+            // The 32 rows of a chunk lie in one cache block, stride_token apart.
+            const float4* krow = reinterpret_cast<const float4*>(
+                                     cache_row(a, a.k_cache, it.b, it.hk, t0)) + lane;
+            const float4* vrow = reinterpret_cast<const float4*>(
+                                     cache_row(a, a.v_cache, it.b, it.hk, t0)) + lane;
+            const int64_t row_f4 = a.stride_token / 4;
+
+            // Scores: lane j ends up holding the G scores of key t0 + j. Rows are fetched
+            // eight at a time so that their latencies overlap.
             float sc[G];
 #pragma unroll
             for (int n = 0; n < G; ++n) sc[n] = -INFINITY;
-            for (int32_t j0 = 0; j0 < valid; j0 += 4) {
-                float4 kv[4];
+#pragma unroll 1
+            for (int32_t j0 = 0; j0 < valid; j0 += 8) {
+                float4 kv[8];
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
+                for (int jj = 0; jj < 8; ++jj) {
                     kv[jj] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (j0 + jj < valid) {
-                        kv[jj] = __ldg(reinterpret_cast<const float4*>(
-                                           cache_row(a, a.k_cache, it.b, it.hk, t0 + j0 + jj)) + lane);
-                    }
+                    if (j0 + jj < valid) kv[jj] = __ldg(krow + (int64_t)(j0 + jj) * row_f4);
                 }
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
+                for (int jj = 0; jj < 8; ++jj) {
 #pragma unroll
                     for (int n = 0; n < G; ++n) {
                         float part = q[n].x * kv[jj].x + q[n].y * kv[jj].y + q[n].z * kv[jj].z +
@@ -126,14 +132,23 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
                 m[n] = mnew;
             }
 
-            for (int32_t j = 0; j < valid; ++j) {
-                const float4 vv = __ldg(reinterpret_cast<const float4*>(
-                                            cache_row(a, a.v_cache, it.b, it.hk, t0 + j)) + lane);
+#pragma unroll 1
+            for (int32_t j0 = 0; j0 < valid; j0 += 8) {
+                float4 vv[8];
 #pragma unroll
-                for (int n = 0; n < G; ++n) {
-                    const float pj = __shfl_sync(0xffffffffu, p[n], j);
-                    o[n].x += pj * vv.x; o[n].y += pj * vv.y;
-                    o[n].z += pj * vv.z; o[n].w += pj * vv.w;
+                for (int jj = 0; jj < 8; ++jj) {
+                    vv[jj] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (j0 + jj < valid) vv[jj] = __ldg(vrow + (int64_t)(j0 + jj) * row_f4);
+                }
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) {
+#pragma unroll
+                    for (int n = 0; n < G; ++n) {
+                        // Keys past the end have p = 0 and a zero row.
+                        const float pj = __shfl_sync(0xffffffffu, p[n], (j0 + jj) & 31);
+                        o[n].x += pj * vv[jj].x; o[n].y += pj * vv[jj].y;
+                        o[n].z += pj * vv[jj].z; o[n].w += pj * vv[jj].w;
+                    }
                 }
             }
         }

@@ -139,6 +139,7 @@ struct PlanInput {
     int32_t split_keys;
     size_t workspace_bytes;  // 0 = unconstrained
     int32_t chunk_align;     // splits start on multiples of this many chunks
+    double overhead_scale;   // fixed costs relative to one step (a CUDA-core FP32 step is long)
 };
 
 int64_t items_for(const PlanInput& in, int32_t q, int32_t* max_splits) {
@@ -205,8 +206,9 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
         const int64_t items = items_for(in, q, &ms);
         if (in.workspace_bytes != 0 && ms > 1 && (size_t)items * rec > in.workspace_bytes) break;
         const int64_t rounds = (items + g_max - 1) / g_max;
-        double cost = (double)rounds * ((double)ceil_div(q, kPlanWarps) + kItemOverhead);
-        if (ms > 1) cost += kCombineBase + kCombinePerSplit * ms;
+        double cost = (double)rounds *
+                      ((double)ceil_div(q, kPlanWarps) + in.overhead_scale * kItemOverhead);
+        if (ms > 1) cost += in.overhead_scale * (kCombineBase + kCombinePerSplit * ms);
         if (!have || cost < best_cost - 1e-9) {
             best_cost = cost;
             best_q = q;
@@ -237,6 +239,9 @@ int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pl
     in.workspace_bytes = p->workspace != nullptr ? p->workspace_bytes : 0;
     const int32_t stage_keys = p->dtype == GQA_DTYPE_BF16 ? stream_shape().keys : kChunkKeys;
     in.chunk_align = stage_keys > kChunkKeys ? stage_keys / kChunkKeys : 1;
+    // The FP32 kernel spends roughly ten times longer on a chunk than the BF16 one, so the
+    // fixed costs weigh a tenth as much there and finer splits pay off.
+    in.overhead_scale = p->dtype == GQA_DTYPE_F32 ? 0.1 : 1.0;
     if (p->block_table_dev != nullptr && p->blocks_per_seq > 1 &&
         p->layout.block_tokens % stage_keys != 0) {
         return GQA_ERR_SHAPE;
