@@ -466,7 +466,7 @@ def run_ours(args) -> None:
                      "traffic_source": "ncu capture of the batch-1 case, scaled by bytes"},
         "e2e": {"value": e2e_us, "unit": "us/layer", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
-        "gpu_launches": 3 * steps,
+        "gpu_launches": (4 if comm is not None and args.gather == "peer" else 3) * steps,
         "clocks": clock_info,
     }
     if rank == 0 and world == 1 and not args.no_cpu:
