@@ -255,7 +255,18 @@ def run_ours(args) -> None:
         dist.broadcast_object_list(ident, src=0)
         comm = gqa.ShardComm(ident[0], world, rank)
         if args.gather == "peer":
-            comm.enable_peer_gather(1 << 20)
+            # Needs CUDA IPC between the ranks' processes; every rank falls back to NCCL
+            # together if any of them cannot set it up.
+            try:
+                comm.enable_peer_gather(1 << 20)
+                ok = 1
+            except gqa.GqaError:
+                ok = 0
+            flag = torch.tensor([ok], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0:
+                args.gather = "nccl"
+                comm.disable_peer_gather()
 
     hq_total, hkv_total, lens, layout_kind, dtype_name = WORKLOADS[args.workload]
     batch = len(lens)

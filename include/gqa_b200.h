@@ -333,6 +333,8 @@ int gqa_comm_all_gather(gqa_comm* comm, const void* send, void* recv, size_t byt
  * of ncclAllGather. Synchronises the device. At most 8 ranks.
  */
 int gqa_comm_enable_peer_gather(gqa_comm* comm, size_t max_bytes_per_rank);
+/* Back to ncclAllGather (every rank must do the same); frees the window. */
+void gqa_comm_disable_peer_gather(gqa_comm* comm);
 /*
  * One gather step with peer stores on `stream`: recv is [nranks][bytes]; bytes is a multiple
  * of 16 and both buffers are 16-byte aligned. Collective (every rank calls it once per step,

@@ -139,6 +139,7 @@ _SIGNATURES = {
     "gqa_comm_nranks": (C.c_int32, [C.c_void_p]),
     "gqa_comm_all_gather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "gqa_comm_enable_peer_gather": (C.c_int, [C.c_void_p, C.c_size_t]),
+    "gqa_comm_disable_peer_gather": (None, [C.c_void_p]),
     "gqa_comm_peer_gather": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                        C.c_void_p, C.c_void_p]),
     "gqa_comm_unique_id": (C.c_int, [C.c_void_p]),
@@ -490,6 +491,9 @@ class ShardComm:
         """Collective: from now on decode_sharded gathers with peer stores over NVLink."""
         _check(lib().gqa_comm_enable_peer_gather(self._h, max_bytes_per_rank),
                "gqa_comm_enable_peer_gather")
+
+    def disable_peer_gather(self) -> None:
+        lib().gqa_comm_disable_peer_gather(self._h)
 
     def all_gather(self, send: torch.Tensor, recv: torch.Tensor,
                    stream: Optional[int] = None) -> None:

@@ -309,18 +309,21 @@ int gqa_comm_peer_gather(gqa_comm* comm, const void* send, void* recv, size_t by
     return e == cudaSuccess ? GQA_OK : GQA_ERR_CUDA;
 }
 
+void gqa_comm_disable_peer_gather(gqa_comm* comm) {
+    if (comm == nullptr || comm->window_local == nullptr) return;
+    cudaDeviceSynchronize();
+    for (int p = 0; p < comm->nranks; ++p) {
+        if (p != comm->rank && comm->windows[p] != nullptr) cudaIpcCloseMemHandle(comm->windows[p]);
+        comm->windows[p] = nullptr;
+    }
+    cudaFree(comm->window_local);
+    comm->window_local = nullptr;
+    comm->slot_bytes = 0;
+}
+
 void gqa_comm_destroy(gqa_comm* comm) {
     if (comm == nullptr) return;
-    if (comm->window_local != nullptr) {
-        cudaDeviceSynchronize();
-        for (int p = 0; p < comm->nranks; ++p) {
-            if (p != comm->rank && comm->windows[p] != nullptr) {
-                cudaIpcCloseMemHandle(comm->windows[p]);
-            }
-        }
-        cudaFree(comm->window_local);
-        comm->window_local = nullptr;
-    }
+    gqa_comm_disable_peer_gather(comm);
     const NcclApi& api = nccl();
     if (api.ok && comm->comm != nullptr) api.comm_destroy(comm->comm);
     delete comm;

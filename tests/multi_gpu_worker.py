@@ -20,6 +20,33 @@ from llminfer_b200 import sharding  # noqa: E402
 from oracle import oracle  # noqa: E402
 
 
+def missing_peer_case(comm, rank, world, dev) -> None:
+    """A rank that does not show up for a gather step: the others' wait runs out after its
+    time limit, the status word says so, nothing hangs and the GPU stays usable. The absent
+    rank simply skips the call (it is between steps, with nothing in flight)."""
+    import time
+    comm.enable_peer_gather(4096)
+    send = torch.full((1024,), rank + 1, dtype=torch.int32, device=dev)
+    recv = torch.zeros(world, 1024, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for _ in range(2):  # healthy steps first
+        comm.peer_gather(send, recv, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and recv[:, 0].tolist() == list(range(1, world + 1))
+    dist.barrier()
+    if rank != world - 1:  # the last rank stays away from the third step
+        t0 = time.perf_counter()
+        comm.peer_gather(send, recv, status)
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t0
+        assert int(status.item()) == 2, status.item()
+        assert 1.5 <= waited <= 10.0, waited
+        # The context is intact: ordinary work still runs.
+        check = torch.arange(16, device=dev).sum().item()
+        assert check == 120
+    dist.barrier()
+
+
 def main() -> None:
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -28,6 +55,14 @@ def main() -> None:
     ident = [gqa.ShardComm.unique_id() if rank == 0 else None]
     dist.broadcast_object_list(ident, src=0)
     comm = gqa.ShardComm(ident[0], world, rank)
+
+    if "--timeout-case" in sys.argv:
+        missing_peer_case(comm, rank, world, dev)
+        comm.close()
+        dist.destroy_process_group()
+        if rank == 0:
+            print("multi_gpu_worker ok")
+        return
 
     hq, hkv, batch, block_tokens, d = 64, 8, 3, 256, 128
     lens = [3000, 257, 1024]
