@@ -480,6 +480,22 @@ def run_ours(args) -> None:
         "gpu_launches": (4 if comm is not None and args.gather == "peer" else 3) * steps,
         "clocks": clock_info,
     }
+    if rank == 0 and world == 1 and args.sweep:
+        # The other BASELINE configurations, attention kernels only, each in its own process.
+        sweep = {}
+        for name in WORKLOADS:
+            if name == args.workload:
+                continue
+            run = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--workload", name,
+                                  "--attn-only", "--no-cpu", "--steps", str(steps)],
+                                 capture_output=True, text=True)
+            try:
+                got = json.loads(run.stdout.strip().splitlines()[-1])
+                sweep[name] = {"attention_only_us_per_layer": got["attention_only_us_per_layer"],
+                               "gbs": got["roofline"]["achieved"]}
+            except (IndexError, ValueError, KeyError):
+                sweep[name] = {"error": run.stderr[-200:]}
+        line["context_sweep"] = sweep
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_sample_us_per_layer(hq_total, hkv_total, lens, reps=2, warmup=1)
         line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -499,6 +515,8 @@ def main() -> None:
     ap.add_argument("--workload", choices=tuple(WORKLOADS), default=DEFAULT_WORKLOAD)
     ap.add_argument("--gather", choices=("peer", "nccl"), default="peer",
                     help="N > 1: gather the output with peer stores over NVLink or with NCCL")
+    ap.add_argument("--sweep", action="store_true",
+                    help="N = 1: also time the attention kernels on the other workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-graph", action="store_true",
                     help="time eager launches instead of a CUDA-graph replay (profiler runs)")

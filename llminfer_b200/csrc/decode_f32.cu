@@ -9,7 +9,7 @@
 //
 // The combine kernel takes the place of flashdecoding_gqa_combine_kernel
 // (code/source/op/kernel/cuda/mha_kernel.cu:399-438): out = sum_s O_s 2^(m_s - M) /
-// sum_s l_s 2^(m_s - M), splits merged in ascending order.
+// sum_s l_s 2^(m_s - M), splits added in a fixed order.
 #include "decode_kernels.cuh"
 #include "ptx.cuh"
 #include "work_map.cuh"

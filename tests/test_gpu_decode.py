@@ -130,7 +130,7 @@ def test_bf16_split_is_deterministic_in_grid_size(gqa):
     assert np.array_equal(a, b)
 
 
-@pytest.mark.parametrize("group", [1, 2, 3, 4, 5, 8])
+@pytest.mark.parametrize("group", [1, 2, 3, 4, 5, 6, 7, 8])
 def test_bf16_group_sizes(gqa, group):
     rng = np.random.default_rng(100 + group)
     hkv, length, max_seq_len = 4, 700, 704
@@ -305,3 +305,84 @@ def test_bf16_long_context_properties(gqa):
     gqa.decode(q, k, v, out, num_kv_heads=hkv, layout=layout, seq_lens=[length], workspace=ws)
     expect = row.view(hkv, 1, H.D).expand(hkv, hq // hkv, H.D).reshape(hq, H.D).float()
     assert torch.allclose(out[0].float(), expect, atol=0, rtol=2 ** -7)
+
+
+def test_bf16_many_short_sequences_lengths_on_device_only(gqa):
+    """64 sequences from 1 to 700 keys, lengths known on the device only (the host plans from a
+    hint), 64-token pool blocks."""
+    rng = np.random.default_rng(59)
+    batch, hq, hkv, block_tokens = 64, 16, 4, 64
+    lens = [int(x) for x in rng.integers(1, 701, size=batch)]
+    lens[0], lens[1], lens[2], lens[3] = 1, 64, 65, 700
+    layout, q, k_pool, v_pool, table = make_paged_batch(gqa, rng, batch, hq, hkv, lens, block_tokens)
+    want = oracle.gqa_decode(q, k_pool, v_pool, lens, hkv=hkv, stride_block=layout.stride_block,
+                             stride_token=layout.stride_token, stride_head=layout.stride_head,
+                             block_tokens=block_tokens, block_table=np.maximum(table, 0))
+    out = torch.full((batch, hq, H.D), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+    ws = gqa.binding.workspace_for(batch, hq, hkv, "cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    gqa.decode(H.bf16_tensor(q), H.bf16_tensor(k_pool), H.bf16_tensor(v_pool), out,
+               num_kv_heads=hkv, layout=layout, seq_lens=None,
+               seq_lens_dev=torch.tensor(lens, dtype=torch.int32, device="cuda:0"),
+               block_table=torch.from_numpy(table).to("cuda:0"), workspace=ws, status=status,
+               plan_len_hint=256)
+    got = H.f32_of(out)
+    assert np.isfinite(got).all() and int(status.item()) == 0
+    abs_err, rel_err = H.errors(got, want)
+    assert abs_err <= ABS_TOL_BF16 and rel_err <= REL_TOL_BF16, (abs_err, rel_err)
+
+
+def test_bf16_full_size_long_context_batch(gqa):
+    """The benchmark's shape at full size (64 q / 8 kv heads, batch 4, 131072 keys, 2 GiB of
+    K and V in 256-token pool blocks): size-independent properties, and one (sequence, kv head)
+    against the oracle."""
+    torch.manual_seed(61)
+    dev = "cuda:0"
+    batch, hq, hkv, length, block_tokens = 4, 64, 8, 131072, 256
+    blocks_per_seq = length // block_tokens
+    num_blocks = batch * blocks_per_seq
+    layout = gqa.layout_pool(num_blocks, block_tokens, hkv)
+    elems = num_blocks * hkv * block_tokens * H.D
+    k_pool = torch.empty(elems, dtype=torch.bfloat16, device=dev)
+    v_pool = torch.empty(elems, dtype=torch.bfloat16, device=dev)
+    for pool in (k_pool, v_pool):
+        for start in range(0, elems, 1 << 26):
+            n = min(1 << 26, elems - start)
+            pool[start:start + n] = torch.randn(n, device=dev).to(torch.bfloat16)
+    table = torch.randperm(num_blocks).to(torch.int32).view(batch, blocks_per_seq).to(dev)
+    q = torch.randn(batch, hq, H.D, device=dev).to(torch.bfloat16)
+    lens = [length] * batch
+    lens_dev = torch.tensor(lens, dtype=torch.int32, device=dev)
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev).view(torch.float32)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def run(split_keys=0):
+        out = torch.full((batch, hq, H.D), float("nan"), dtype=torch.bfloat16, device=dev)
+        gqa.decode(q, k_pool, v_pool, out, num_kv_heads=hkv, layout=layout, seq_lens=lens,
+                   seq_lens_dev=lens_dev, block_table=table, workspace=ws, status=status,
+                   split_keys=split_keys)
+        torch.cuda.synchronize()
+        return out
+
+    auto = run()
+    assert torch.isfinite(auto.float()).all() and int(status.item()) == 0
+    # How the keys are cut must not matter beyond rounding.
+    other = run(split_keys=8192)
+    scale = auto.float().abs().max().item()
+    assert (auto.float() - other.float()).abs().max().item() <= REL_TOL_BF16 * scale
+    # One unit against the oracle: sequence 2, kv head 5 (query heads 40..47).
+    b, hk, g = 2, 5, hq // hkv
+    blocks = table[b].long()
+    k_unit = k_pool.view(num_blocks, hkv, block_tokens, H.D)[blocks, hk].reshape(length, H.D)
+    v_unit = v_pool.view(num_blocks, hkv, block_tokens, H.D)[blocks, hk].reshape(length, H.D)
+    want = oracle.gqa_decode(H.bits_of(q[b:b + 1, hk * g:(hk + 1) * g]), H.bits_of(k_unit).reshape(-1),
+                             H.bits_of(v_unit).reshape(-1), [length], hkv=1,
+                             stride_block=length * H.D, stride_token=H.D, stride_head=H.D,
+                             block_tokens=length)
+    abs_err, rel_err = H.errors(H.f32_of(auto[b, hk * g:(hk + 1) * g]), want[0])
+    assert abs_err <= ABS_TOL_BF16 and rel_err <= REL_TOL_BF16, (abs_err, rel_err)
+    # Identical V rows: the weights sum to one, so every head returns that row.
+    row = torch.randn(H.D, device=dev).to(torch.bfloat16)
+    v_pool.view(-1, H.D)[:] = row
+    same = run()
+    assert torch.allclose(same.float(), row.float().expand_as(same), atol=0, rtol=2 ** -7)
