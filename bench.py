@@ -449,6 +449,18 @@ def run_ours(args) -> None:
     h2d = (hq + 2 * hkv) * HEAD_DIM * 2 * batch + 8 * batch
     d2h = out_host.numel() * 2
 
+    # Front stage, streaming kernel, combine; the gather is a fourth launch unless the combine
+    # kernel carries it (peer gather, split units, every combine CTA resident at once).
+    peer = comm is not None and args.gather == "peer"
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    fused_gather = (peer and plan["needs_combine"] and batch * hq <= min(160, sms)
+                    and os.environ.get("GQA_FUSED_GATHER", "1")[:1] != "0")
+    launches_per_step = 3 + (1 if world > 1 and not fused_gather else 0)
+    gather_note = ""
+    if world > 1:
+        gather_note = (", peer-store all-gather over NVLink inside the combine kernel"
+                       if fused_gather else f", {args.gather} all-gather over NVLink")
+
     peak, peak_kind = measured_peak_gbs()
     rank_bytes = algorithmic_bytes(hq, hkv, lens, elem)
     achieved = rank_bytes / (attn_us * 1e-6) / 1e9
@@ -464,7 +476,7 @@ def run_ours(args) -> None:
                    "l2": f"inputs larger than L2: {slots} cache slot(s) of "
                          f"{slot_bytes / 2**20:.0f} MiB cycled per GPU",
                    "step": "qk-norm+rope+append, split attention, lse combine"
-                           + (f", {args.gather} all-gather over NVLink" if world > 1 else ""),
+                           + gather_note,
                    "split_chunks": plan["split_chunks"], "ctas": plan["num_ctas"],
                    "items": plan["num_items"]},
         "hbm_tbs_aggregate": achieved * world / 1e3,
@@ -477,7 +489,7 @@ def run_ours(args) -> None:
                      "traffic_source": "ncu capture of the batch-1 case, scaled by bytes"},
         "e2e": {"value": e2e_us, "unit": "us/layer", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
-        "gpu_launches": (4 if comm is not None and args.gather == "peer" else 3) * steps,
+        "gpu_launches": launches_per_step * steps,
         "clocks": clock_info,
     }
     if rank == 0 and world == 1 and args.sweep:

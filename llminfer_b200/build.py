@@ -29,7 +29,8 @@ KERNEL_SOURCES = [
     "csrc/kv_pool.cpp",
     "csrc/shard_comm.cu",
 ]
-KERNEL_HEADERS = ["csrc/ptx.cuh", "csrc/work_map.cuh", "csrc/decode_kernels.cuh"]
+KERNEL_HEADERS = ["csrc/ptx.cuh", "csrc/work_map.cuh", "csrc/decode_kernels.cuh",
+                  "csrc/peer_window.cuh"]
 
 
 def _stale(output: Path, inputs: list[Path]) -> bool:

@@ -10,7 +10,10 @@
 // The combine kernel takes the place of flashdecoding_gqa_combine_kernel
 // (code/source/op/kernel/cuda/mha_kernel.cu:399-438): out = sum_s O_s 2^(m_s - M) /
 // sum_s l_s 2^(m_s - M), splits added in a fixed order.
+#include <cstring>
+
 #include "decode_kernels.cuh"
+#include "peer_window.cuh"
 #include "ptx.cuh"
 #include "work_map.cuh"
 
@@ -196,6 +199,7 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
     }
 }
 
+constexpr int kCombineWideGrid = 160;  // largest grid that runs with 4 lanes per channel
 constexpr int kCombineTile = 32;   // splits merged per pass
 constexpr int kCombineSlots = 8;   // partial sums per channel per pass, whatever the CTA width
 
@@ -209,8 +213,17 @@ constexpr int kCombineSlots = 8;   // partial sums per channel per pass, whateve
 // is used, so a pass costs one trip to L2; longer split lists fold pass by pass with a running
 // (M, L). Partial records are read with L1-bypassing loads: the kernel that wrote them may
 // still have been running when this one started.
-template <bool BF16_OUT, int LANES>
-__global__ void __launch_bounds__(kHeadDim * LANES) gqa_decode_combine(const DecodeArgs a) {
+//
+// GATHER adds the exchange between the GPUs of a KV-head-parallel node to the same kernel:
+// each CTA pushes its finished row, as step-tagged 8-byte words, into its place in every
+// rank's peer window with plain stores over NVLink, then polls (with a time limit) the same
+// row of every rank in its own window and writes them to the gathered output. A row leaves as
+// soon as it is merged, so the transfer of the first rows overlaps the merge of the others and
+// the separate gather launch goes away. Units that were not split are pushed from the output
+// the streaming kernel wrote. Used only when every CTA of the grid is resident at once.
+template <bool BF16_OUT, int LANES, bool GATHER>
+__global__ void __launch_bounds__(kHeadDim * LANES)
+    gqa_decode_combine(const DecodeArgs a, const PeerGatherArgs g) {
     constexpr int kOwn = kCombineSlots / LANES;            // slots per thread
     constexpr int kPerSlot = kCombineTile / kCombineSlots;  // splits per slot per pass
     extern __shared__ int32_t s_tables[];
@@ -229,87 +242,155 @@ __global__ void __launch_bounds__(kHeadDim * LANES) gqa_decode_combine(const Dec
     const int32_t n = h - hk * group;
     int32_t first, nsplits;
     unit_items(a, tables, b, hk, &first, &nsplits);
-    if (nsplits <= 1) return;  // the streaming kernel already wrote the final output
+    // Not split: the streaming kernel already wrote the final output.
+    if (!GATHER && nsplits <= 1) return;
 
     const int d = threadIdx.x & (kHeadDim - 1);
     const int j = threadIdx.x >> 7;
-    const int64_t rec_floats = (int64_t)group * (kHeadDim + 2);
-    const float* rec0 = a.workspace + (int64_t)first * rec_floats;
-    const float* m_base = rec0 + group * kHeadDim + n;
-    const float* l_base = m_base + group;
-    const float* o_base = rec0 + n * kHeadDim + d;
+    const int64_t o_idx = ((int64_t)b * a.num_q_heads + h) * kHeadDim + d;
+    float result = 0.f;  // the finished channel, held by the threads with j == 0
+    if (nsplits > 1) {
+        const int64_t rec_floats = (int64_t)group * (kHeadDim + 2);
+        const float* rec0 = a.workspace + (int64_t)first * rec_floats;
+        const float* m_base = rec0 + group * kHeadDim + n;
+        const float* l_base = m_base + group;
+        const float* o_base = rec0 + n * kHeadDim + d;
 
-    float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
-    for (int32_t base = 0; base < nsplits; base += kCombineTile) {
-        const int32_t cnt = min(kCombineTile, nsplits - base);
-        float o[kOwn][kPerSlot];
-        float ml[kOwn][kPerSlot];
-#pragma unroll
-        for (int t = 0; t < kOwn; ++t) {
-#pragma unroll
-            for (int r = 0; r < kPerSlot; ++r) {
-                const int32_t s = (j + t * LANES) + r * kCombineSlots;
-                o[t][r] = 0.f;
-                ml[t][r] = 0.f;
-                if (s < cnt) {
-                    const int64_t off = (int64_t)(base + s) * rec_floats;
-                    o[t][r] = __ldcg(o_base + off);
-                    if (d == 0) ml[t][r] = __ldcg(m_base + off);
-                    if (d == 1) ml[t][r] = __ldcg(l_base + off);
-                }
-            }
-        }
-        if (d < 2) {
+        float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
+        for (int32_t base = 0; base < nsplits; base += kCombineTile) {
+            const int32_t cnt = min(kCombineTile, nsplits - base);
+            float o[kOwn][kPerSlot];
+            float ml[kOwn][kPerSlot];
 #pragma unroll
             for (int t = 0; t < kOwn; ++t) {
 #pragma unroll
                 for (int r = 0; r < kPerSlot; ++r) {
                     const int32_t s = (j + t * LANES) + r * kCombineSlots;
-                    if (s < cnt) (d == 0 ? s_m : s_l)[s] = ml[t][r];
+                    o[t][r] = 0.f;
+                    ml[t][r] = 0.f;
+                    if (s < cnt) {
+                        const int64_t off = (int64_t)(base + s) * rec_floats;
+                        o[t][r] = __ldcg(o_base + off);
+                        if (d == 0) ml[t][r] = __ldcg(m_base + off);
+                        if (d == 1) ml[t][r] = __ldcg(l_base + off);
+                    }
                 }
             }
-        }
-        __syncthreads();
-        float tmax = s_m[0];
-        for (int32_t i = 1; i < cnt; ++i) tmax = fmaxf(tmax, s_m[i]);
-        const float m_new = fmaxf(m_run, tmax);
-        const float rescale = BF16_OUT ? ex2_approx(m_run - m_new) : exp2f(m_run - m_new);
-        float ltile = 0.f;
-        for (int32_t i = 0; i < cnt; ++i) {
-            const float w = BF16_OUT ? ex2_approx(s_m[i] - m_new) : exp2f(s_m[i] - m_new);
-            ltile += s_l[i] * w;
-        }
+            if (d < 2) {
 #pragma unroll
-        for (int t = 0; t < kOwn; ++t) {
-            float part = 0.f;
+                for (int t = 0; t < kOwn; ++t) {
 #pragma unroll
-            for (int r = 0; r < kPerSlot; ++r) {
-                const int32_t s = (j + t * LANES) + r * kCombineSlots;
-                if (s < cnt) {
-                    const float w = BF16_OUT ? ex2_approx(s_m[s] - m_new) : exp2f(s_m[s] - m_new);
-                    part += o[t][r] * w;
+                    for (int r = 0; r < kPerSlot; ++r) {
+                        const int32_t s = (j + t * LANES) + r * kCombineSlots;
+                        if (s < cnt) (d == 0 ? s_m : s_l)[s] = ml[t][r];
+                    }
                 }
             }
-            s_part[j + t * LANES][d] = part;
+            __syncthreads();
+            float tmax = s_m[0];
+            for (int32_t i = 1; i < cnt; ++i) tmax = fmaxf(tmax, s_m[i]);
+            const float m_new = fmaxf(m_run, tmax);
+            const float rescale = BF16_OUT ? ex2_approx(m_run - m_new) : exp2f(m_run - m_new);
+            float ltile = 0.f;
+            for (int32_t i = 0; i < cnt; ++i) {
+                const float w = BF16_OUT ? ex2_approx(s_m[i] - m_new) : exp2f(s_m[i] - m_new);
+                ltile += s_l[i] * w;
+            }
+#pragma unroll
+            for (int t = 0; t < kOwn; ++t) {
+                float part = 0.f;
+#pragma unroll
+                for (int r = 0; r < kPerSlot; ++r) {
+                    const int32_t s = (j + t * LANES) + r * kCombineSlots;
+                    if (s < cnt) {
+                        const float w = BF16_OUT ? ex2_approx(s_m[s] - m_new) : exp2f(s_m[s] - m_new);
+                        part += o[t][r] * w;
+                    }
+                }
+                s_part[j + t * LANES][d] = part;
+            }
+            __syncthreads();
+            if (j == 0) {
+                float tile_acc = s_part[0][d];
+#pragma unroll
+                for (int v = 1; v < kCombineSlots; ++v) tile_acc += s_part[v][d];
+                acc = acc * rescale + tile_acc;
+            }
+            l_run = l_run * rescale + ltile;
+            m_run = m_new;
+            __syncthreads();  // the next pass overwrites s_m, s_l and s_part
         }
-        __syncthreads();
+        timeline_mark(7, a.fixed_block);
         if (j == 0) {
-            float tile_acc = s_part[0][d];
-#pragma unroll
-            for (int v = 1; v < kCombineSlots; ++v) tile_acc += s_part[v][d];
-            acc = acc * rescale + tile_acc;
+            result = acc / l_run;
+            if (BF16_OUT) {
+                reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(result);
+            } else {
+                reinterpret_cast<float*>(a.out)[o_idx] = result;
+            }
         }
-        l_run = l_run * rescale + ltile;
-        m_run = m_new;
-        __syncthreads();  // the next pass overwrites s_m, s_l and s_part
+    } else if (GATHER && j == 0) {
+        result = BF16_OUT ? __bfloat162float(__ldcg(reinterpret_cast<const __nv_bfloat16*>(a.out) + o_idx))
+                          : __ldcg(reinterpret_cast<const float*>(a.out) + o_idx);
     }
-    timeline_mark(7, a.fixed_block);
+    if (!GATHER) return;
+
+    // ---- exchange of the row with the other ranks ----
+    constexpr int kRowWords = BF16_OUT ? kHeadDim / 2 : kHeadDim;
+    __shared__ uint32_t s_row[kRowWords];
+    __shared__ uint32_t s_step;
+    __shared__ int s_timed_out;
+    uint8_t* mine = g.windows[g.rank];
+    WindowCtrl* ctrl = window_ctrl(mine, g.slot_bytes, g.nranks);
     if (j == 0) {
-        const int64_t o_idx = ((int64_t)b * a.num_q_heads + h) * kHeadDim + d;
         if (BF16_OUT) {
-            reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(acc / l_run);
+            const uint32_t bits = __bfloat16_as_ushort(__float2bfloat16(result));
+            const uint32_t next = __shfl_down_sync(0xffffffffu, bits, 1);
+            if ((d & 1) == 0) s_row[d >> 1] = bits | (next << 16);
         } else {
-            reinterpret_cast<float*>(a.out)[o_idx] = acc / l_run;
+            s_row[d] = __float_as_uint(result);
+        }
+    }
+    if (threadIdx.x == 0) {
+        s_step = *reinterpret_cast<volatile uint32_t*>(&ctrl->step) + 1;
+        s_timed_out = 0;
+    }
+    __syncthreads();
+    const uint32_t step = s_step;
+    const uint64_t row_off = (uint64_t)blockIdx.x * kRowWords;
+    const int total = kRowWords * g.nranks;
+    for (int i = threadIdx.x; i < total; i += kHeadDim * LANES) {
+        const int p = i / kRowWords;
+        const int w = i - p * kRowWords;
+        push_word(window_slot(g.windows[p], step, g.nranks, g.rank, g.slot_bytes) + row_off + w,
+                  step, s_row[w]);
+    }
+    const unsigned long long start = global_timer();
+    bool timed_out = false;
+    for (int i = threadIdx.x; i < total && !timed_out; i += kHeadDim * LANES) {
+        const int p = i / kRowWords;
+        const int w = i - p * kRowWords;
+        uint32_t data;
+        if (poll_word(window_slot(mine, step, g.nranks, p, g.slot_bytes) + row_off + w, step,
+                      start, &data)) {
+            g.recv[(uint64_t)p * g.words + row_off + w] = data;
+        } else {
+            timed_out = true;
+        }
+    }
+    if (timed_out) s_timed_out = 1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (s_timed_out) {
+            ctrl->status = 1;
+            if (g.status != nullptr) atomicExch(g.status, 2);
+        }
+        // The last CTA to finish advances the step counter for the next launch.
+        __threadfence();
+        const uint32_t ticket = atomicAdd(&ctrl->ticket_out, 1u);
+        if (ticket == gridDim.x - 1) {
+            ctrl->ticket_out = 0;
+            ctrl->step = step;
         }
     }
 }
@@ -325,21 +406,37 @@ cudaError_t launch_stream_f32(const DecodeArgs& args, int grid, cudaStream_t str
     return launch_pdl(gqa_decode_stream_f32<8>, dim3(grid), dim3(kF32Threads), smem, stream, args);
 }
 
-cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t stream) {
+cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t stream,
+                           const PeerGatherArgs* gather) {
     const size_t smem =
         args.seq_lens_dev != nullptr ? 2 * ((size_t)args.batch + 1) * sizeof(int32_t) : 0;
     const int grid = args.batch * args.num_q_heads;
-    const bool wide = grid <= 160;
-    if (bf16_out) {
-        return wide ? launch_pdl(gqa_decode_combine<true, 4>, dim3(grid), dim3(kHeadDim * 4), smem,
-                                 stream, args)
-                    : launch_pdl(gqa_decode_combine<true, 2>, dim3(grid), dim3(kHeadDim * 2), smem,
-                                 stream, args);
+    const bool wide = grid <= kCombineWideGrid;
+    PeerGatherArgs g;
+    std::memset(&g, 0, sizeof(g));
+    if (gather != nullptr) {
+        if (!wide) return cudaErrorInvalidValue;  // the caller checks combine_can_gather()
+        g = *gather;
+        return bf16_out ? launch_pdl(gqa_decode_combine<true, 4, true>, dim3(grid),
+                                     dim3(kHeadDim * 4), smem, stream, args, g)
+                        : launch_pdl(gqa_decode_combine<false, 4, true>, dim3(grid),
+                                     dim3(kHeadDim * 4), smem, stream, args, g);
     }
-    return wide ? launch_pdl(gqa_decode_combine<false, 4>, dim3(grid), dim3(kHeadDim * 4), smem,
-                             stream, args)
-                : launch_pdl(gqa_decode_combine<false, 2>, dim3(grid), dim3(kHeadDim * 2), smem,
-                             stream, args);
+    if (bf16_out) {
+        return wide ? launch_pdl(gqa_decode_combine<true, 4, false>, dim3(grid),
+                                 dim3(kHeadDim * 4), smem, stream, args, g)
+                    : launch_pdl(gqa_decode_combine<true, 2, false>, dim3(grid),
+                                 dim3(kHeadDim * 2), smem, stream, args, g);
+    }
+    return wide ? launch_pdl(gqa_decode_combine<false, 4, false>, dim3(grid), dim3(kHeadDim * 4),
+                             smem, stream, args, g)
+                : launch_pdl(gqa_decode_combine<false, 2, false>, dim3(grid), dim3(kHeadDim * 2),
+                             smem, stream, args, g);
+}
+
+bool combine_can_gather(int batch, int num_q_heads, int sm_count) {
+    const int grid = batch * num_q_heads;
+    return grid <= kCombineWideGrid && grid <= sm_count;
 }
 
 }  // namespace gqa

@@ -6,6 +6,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include "../../include/gqa_b200.h"
 #include "work_map.cuh"
 
 namespace gqa {
@@ -30,8 +31,18 @@ cudaError_t launch_stream_bf16(const StreamShape& shape, const CUtensorMap& tmap
 
 cudaError_t launch_stream_f32(const DecodeArgs& args, int grid, cudaStream_t stream);
 
-// One CTA per (sequence, query head); merges the partial records of split units.
-cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t stream);
+struct PeerGatherArgs;
+
+// One CTA per (sequence, query head); merges the partial records of split units. With
+// `gather` the same kernel also exchanges the finished rows with the other ranks of a
+// KV-head-parallel node through their peer windows (allowed when combine_can_gather()).
+cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t stream,
+                           const PeerGatherArgs* gather = nullptr);
+bool combine_can_gather(int batch, int num_q_heads, int sm_count);
+
+// gqa_decode with the gather fused into the combine kernel when that is possible; *fused
+// tells whether it was (if not, nothing was exchanged and the caller gathers separately).
+int decode_with_gather(const gqa_decode_params* p, const PeerGatherArgs* gather, bool* fused);
 
 struct FrontArgs {
     const void* q;

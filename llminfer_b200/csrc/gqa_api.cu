@@ -14,6 +14,7 @@
 #include <cudaTypedefs.h>
 
 #include "decode_kernels.cuh"
+#include "peer_window.cuh"
 #include "work_map.cuh"
 
 namespace {
@@ -445,7 +446,13 @@ int gqa_decode_plan(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pla
     return plan_from_params(p, sm_count, out);
 }
 
-int gqa_decode(const gqa_decode_params* p) {
+int gqa_decode(const gqa_decode_params* p) { return gqa::decode_with_gather(p, nullptr, nullptr); }
+
+}  // extern "C"
+
+int gqa::decode_with_gather(const gqa_decode_params* p, const gqa::PeerGatherArgs* gather,
+                            bool* fused) {
+    if (fused != nullptr) *fused = false;
     int rc = validate_decode(p);
     if (rc != GQA_OK) return rc;
     int32_t sms = 0;
@@ -503,11 +510,16 @@ int gqa_decode(const gqa_decode_params* p) {
     }
     if (e != cudaSuccess) return GQA_ERR_CUDA;
     if (plan.needs_combine) {
-        e = gqa::launch_combine(a, p->dtype == GQA_DTYPE_BF16, stream);
+        const bool fuse =
+            gather != nullptr && gqa::combine_can_gather(p->batch, p->num_q_heads, sms);
+        e = gqa::launch_combine(a, p->dtype == GQA_DTYPE_BF16, stream, fuse ? gather : nullptr);
         if (e != cudaSuccess) return GQA_ERR_CUDA;
+        if (fused != nullptr) *fused = fuse;
     }
     return GQA_OK;
 }
+
+extern "C" {
 
 int gqa_qk_norm_rope_append(const gqa_front_params* p) {
     if (p == nullptr) return GQA_ERR_NULL;

@@ -23,6 +23,7 @@
 // status word and the window's own, and returns: nothing hangs.
 #include "../../include/gqa_b200.h"
 
+#include <cstdlib>
 #include <cstring>
 #include <dlfcn.h>
 #include <mutex>
@@ -32,6 +33,7 @@
 #include <nccl.h>
 
 #include "decode_kernels.cuh"
+#include "peer_window.cuh"
 #include "ptx.cuh"
 
 namespace {
@@ -69,34 +71,12 @@ const NcclApi& nccl() {
 
 namespace {
 
-constexpr int kMaxPeers = 8;
+using gqa::kMaxPeers;
+using gqa::PeerGatherArgs;
+using gqa::WindowCtrl;
+using gqa::window_ctrl;
 constexpr int kGatherCtas = 16;
 constexpr int kGatherThreads = 256;
-constexpr uint64_t kGatherWaitNs = 2000000000ull;
-
-// Control words at the end of a window.
-struct WindowCtrl {
-    uint32_t step;        // completed gathers
-    uint32_t ticket_out;  // CTAs that finished the current gather
-    uint32_t status;      // 1 after a wait ran out
-    uint32_t pad;
-};
-
-struct PeerGatherArgs {
-    uint8_t* windows[kMaxPeers];  // every rank's window as mapped into this process
-    const uint32_t* send;
-    uint32_t* recv;
-    int32_t* status;
-    uint64_t slot_bytes;   // capacity of one slot (payload + step words)
-    uint64_t words;        // 4-byte payload words per rank in this step
-    int32_t nranks;
-    int32_t rank;
-};
-
-__device__ __forceinline__ WindowCtrl* window_ctrl(uint8_t* window, uint64_t slot_bytes,
-                                                   int nranks) {
-    return reinterpret_cast<WindowCtrl*>(window + 2 * (uint64_t)nranks * slot_bytes);
-}
 
 __global__ void __launch_bounds__(kGatherThreads) peer_gather_kernel(const PeerGatherArgs a) {
     __shared__ uint32_t s_step;
@@ -111,7 +91,6 @@ __global__ void __launch_bounds__(kGatherThreads) peer_gather_kernel(const PeerG
     }
     __syncthreads();
     const uint32_t step = s_step;
-    const uint64_t half_off = (uint64_t)(step & 1u) * a.nranks * a.slot_bytes;
     const uint64_t total = a.words * a.nranks;
     const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const uint64_t nthreads = (uint64_t)gridDim.x * blockDim.x;
@@ -120,33 +99,23 @@ __global__ void __launch_bounds__(kGatherThreads) peer_gather_kernel(const PeerG
     for (uint64_t i = tid; i < total; i += nthreads) {
         const int p = (int)(i / a.words);
         const uint64_t w = i - (uint64_t)p * a.words;
-        const unsigned long long word = ((unsigned long long)step << 32) | a.send[w];
-        unsigned long long* dst = reinterpret_cast<unsigned long long*>(
-            a.windows[p] + half_off + (uint64_t)a.rank * a.slot_bytes) + w;
-        asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(dst), "l"(word) : "memory");
+        gqa::push_word(gqa::window_slot(a.windows[p], step, a.nranks, a.rank, a.slot_bytes) + w,
+                       step, a.send[w]);
     }
 
     // 2. every word of every rank's slot in my window, as soon as it shows this step
-    unsigned long long start;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+    const unsigned long long start = gqa::global_timer();
     bool timed_out = false;
     for (uint64_t i = tid; i < total && !timed_out; i += nthreads) {
         const int p = (int)(i / a.words);
         const uint64_t w = i - (uint64_t)p * a.words;
-        const unsigned long long* src = reinterpret_cast<const unsigned long long*>(
-            mine + half_off + (uint64_t)p * a.slot_bytes) + w;
-        unsigned long long word;
-        while (true) {
-            asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word) : "l"(src) : "memory");
-            if ((uint32_t)(word >> 32) == step) break;
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            if (now - start > kGatherWaitNs) {
-                timed_out = true;
-                break;
-            }
+        uint32_t data;
+        if (gqa::poll_word(gqa::window_slot(mine, step, a.nranks, p, a.slot_bytes) + w, step,
+                           start, &data)) {
+            a.recv[(uint64_t)p * a.words + w] = data;
+        } else {
+            timed_out = true;
         }
-        if (!timed_out) a.recv[(uint64_t)p * a.words + w] = (uint32_t)word;
     }
     if (timed_out) s_timed_out = 1;
     __syncthreads();
@@ -176,6 +145,34 @@ struct gqa_comm {
     uint8_t* windows[kMaxPeers];
     size_t slot_bytes;
 };
+
+namespace {
+
+// GQA_FUSED_GATHER=0 keeps the gather in its own kernel (for measurements).
+bool fused_gather_disabled() {
+    static const bool off = [] {
+        const char* v = std::getenv("GQA_FUSED_GATHER");
+        return v != nullptr && v[0] == '0';
+    }();
+    return off;
+}
+
+PeerGatherArgs gather_args(const gqa_comm* comm, const void* send, void* recv, size_t bytes,
+                           int32_t* status_dev) {
+    PeerGatherArgs a;
+    std::memset(&a, 0, sizeof(a));
+    for (int p = 0; p < comm->nranks; ++p) a.windows[p] = comm->windows[p];
+    a.send = static_cast<const uint32_t*>(send);
+    a.recv = static_cast<uint32_t*>(recv);
+    a.status = status_dev;
+    a.slot_bytes = comm->slot_bytes;
+    a.words = bytes / 4;
+    a.nranks = comm->nranks;
+    a.rank = comm->rank;
+    return a;
+}
+
+}  // namespace
 
 extern "C" {
 
@@ -293,16 +290,7 @@ int gqa_comm_peer_gather(gqa_comm* comm, const void* send, void* recv, size_t by
     if ((reinterpret_cast<uintptr_t>(send) | reinterpret_cast<uintptr_t>(recv)) & 15u) {
         return GQA_ERR_ALIGN;
     }
-    PeerGatherArgs a;
-    std::memset(&a, 0, sizeof(a));
-    for (int p = 0; p < comm->nranks; ++p) a.windows[p] = comm->windows[p];
-    a.send = static_cast<const uint32_t*>(send);
-    a.recv = static_cast<uint32_t*>(recv);
-    a.status = status_dev;
-    a.slot_bytes = comm->slot_bytes;
-    a.words = bytes / 4;
-    a.nranks = comm->nranks;
-    a.rank = comm->rank;
+    const PeerGatherArgs a = gather_args(comm, send, recv, bytes, status_dev);
     const cudaError_t e = gqa::launch_pdl(peer_gather_kernel, dim3(kGatherCtas),
                                           dim3(kGatherThreads), 0,
                                           reinterpret_cast<cudaStream_t>(stream), a);
@@ -344,11 +332,24 @@ int gqa_comm_all_gather(gqa_comm* comm, const void* send, void* recv, size_t byt
 
 int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathered) {
     if (p == nullptr || comm == nullptr || gathered == nullptr) return GQA_ERR_NULL;
-    const int rc = gqa_decode(p);
-    if (rc != GQA_OK) return rc;
+    if (p->batch <= 0 || p->num_q_heads <= 0 || p->head_dim <= 0) return GQA_ERR_SHAPE;
     const size_t elem = p->dtype == GQA_DTYPE_F32 ? 4 : 2;
     const size_t bytes = (size_t)p->batch * p->num_q_heads * p->head_dim * elem;
-    if (comm->window_local != nullptr && 2 * bytes <= comm->slot_bytes && bytes % 16 == 0) {
+    const bool peer = comm->window_local != nullptr && 2 * bytes <= comm->slot_bytes &&
+                      bytes % 16 == 0 && p->out != nullptr &&
+                      ((reinterpret_cast<uintptr_t>(p->out) |
+                        reinterpret_cast<uintptr_t>(gathered)) & 15u) == 0;
+    if (peer && !fused_gather_disabled()) {
+        // The combine kernel pushes each row to the peers as soon as it is merged.
+        const PeerGatherArgs g = gather_args(comm, p->out, gathered, bytes, p->status_dev);
+        bool fused = false;
+        const int rc = gqa::decode_with_gather(p, &g, &fused);
+        if (rc != GQA_OK || fused) return rc;
+        return gqa_comm_peer_gather(comm, p->out, gathered, bytes, p->status_dev, p->stream);
+    }
+    const int rc = gqa_decode(p);
+    if (rc != GQA_OK) return rc;
+    if (peer) {
         return gqa_comm_peer_gather(comm, p->out, gathered, bytes, p->status_dev, p->stream);
     }
     return gqa_comm_all_gather(comm, p->out, gathered, bytes, p->stream);

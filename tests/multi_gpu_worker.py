@@ -138,6 +138,27 @@ def main() -> None:
     torch.cuda.current_stream().wait_stream(side)
     assert int(status.item()) == 0
 
+    # FP32 rows through the same gather: sharded equals unsharded bit for bit.
+    hq32, hkv32, len32 = 16, 8, 512
+    q32 = torch.from_numpy(rng.standard_normal((1, hq32, d), dtype=np.float32)).to(dev)
+    k32 = torch.from_numpy(rng.standard_normal((1, len32, hkv32, d), dtype=np.float32)).to(dev)
+    v32 = torch.from_numpy(rng.standard_normal((1, len32, hkv32, d), dtype=np.float32)).to(dev)
+    ws32 = torch.empty(hq32 * 4 * len32, dtype=torch.float32, device=dev)
+    full32 = torch.zeros(1, hq32, d, dtype=torch.float32, device=dev)
+    gqa.decode(q32, k32, v32, full32, num_kv_heads=hkv32, layout=gqa.layout_reference(1, len32, hkv32),
+               seq_lens=[len32], workspace=ws32, split_keys=64)
+    pq32, pkv32 = hq32 // world, hkv32 // world
+    out32 = torch.zeros(1, pq32, d, dtype=torch.float32, device=dev)
+    gathered32 = torch.zeros(world, 1, pq32, d, dtype=torch.float32, device=dev)
+    gqa.decode_sharded(comm, gathered32, q32[:, rank * pq32:(rank + 1) * pq32].contiguous(),
+                       k32[:, :, rank * pkv32:(rank + 1) * pkv32].contiguous(),
+                       v32[:, :, rank * pkv32:(rank + 1) * pkv32].contiguous(), out32,
+                       num_kv_heads=pkv32, layout=gqa.layout_reference(1, len32, pkv32),
+                       seq_lens=[len32], workspace=ws32, split_keys=64)
+    torch.cuda.synchronize()
+    whole32 = sharding.unshard_output(gathered32)
+    assert torch.equal(whole32.view(torch.int32), full32.view(torch.int32)), "fp32 sharded != unsharded"
+
     # The host-buffer step with the gather inside.
     layout_l = gqa.layout_pool(num_blocks, block_tokens, per_kv)
     session = gqa.Session(batch, per_q, per_kv, blocks_per_seq * block_tokens)
