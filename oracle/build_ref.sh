@@ -1,6 +1,7 @@
 #!/usr/bin/env bash
 # Builds oracle/_ref/libref_attn.so: the reference's own CUDA decode-attention path
-# (mha_kernel.cu, rmsnorm_kernel.cu, rope_kernel.cu plus its tensor/buffer/allocator
+# (mha_kernel.cu, rmsnorm_kernel.cu, rope_kernel.cu, the projection GEMVs of
+# matmul_kernel.cu that sit on either side of it, plus its tensor/buffer/allocator
 # sources), compiled from the reference checkout where it lies, for sm_100, against the
 # glog stand-in header in oracle/ref_build/. TEST INFRASTRUCTURE ONLY: it is the
 # second parity checker ("the reference's own attention output"), never shipped or timed
@@ -22,6 +23,7 @@ SRC="$REF/code/source"
     "$SRC/op/kernel/cuda/mha_kernel.cu" \
     "$SRC/op/kernel/cuda/rmsnorm_kernel.cu" \
     "$SRC/op/kernel/cuda/rope_kernel.cu" \
+    "$SRC/op/kernel/cuda/matmul_kernel.cu" \
     "$SRC/tensor/tensor.cpp" \
     "$SRC/base/buffer.cpp" "$SRC/base/alloc.cpp" "$SRC/base/alloc_cpu.cpp" \
     "$SRC/base/alloc_cu.cpp" "$SRC/base/base.cpp" \

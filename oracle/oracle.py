@@ -1,4 +1,5 @@
-"""Python face of the CPU oracle (``oracle/gqa_oracle.c``) and of the reference-kernel build.
+"""Python face of the CPU oracle (``oracle/gqa_oracle.c``, ``oracle/proj_oracle.c``) and of the
+reference-kernel build.
 
 TEST INFRASTRUCTURE ONLY: imported by ``tests/``, ``__graft_entry__.smoke()`` and the
 ``cpu_baseline`` / ``--impl reference`` legs of ``bench.py``. The product never imports it.
@@ -19,6 +20,7 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 LIB = HERE / "liboracle.so"
 SRC = HERE / "gqa_oracle.c"
+SOURCES = [SRC, HERE / "proj_oracle.c"]
 REF_LIB = HERE / "_ref" / "libref_attn.so"
 
 DTYPE_F32 = 0
@@ -28,9 +30,12 @@ _lib: Optional[C.CDLL] = None
 
 
 def build(force: bool = False) -> Path:
-    if force or not LIB.exists() or LIB.stat().st_mtime < SRC.stat().st_mtime:
-        subprocess.run(["gcc", "-O3", "-fopenmp", "-fPIC", "-shared", "-Wall", str(SRC), "-o",
-                        str(LIB), "-lm"], check=True)
+    newest = max(src.stat().st_mtime for src in SOURCES)
+    if force or not LIB.exists() or LIB.stat().st_mtime < newest:
+        # -ffp-contract=off: the restatements spell out every fused multiply-add themselves.
+        subprocess.run(["gcc", "-O3", "-fopenmp", "-fPIC", "-shared", "-Wall",
+                        "-ffp-contract=off", *map(str, SOURCES), "-o", str(LIB), "-lm"],
+                       check=True)
     return LIB
 
 
@@ -67,6 +72,10 @@ def lib() -> C.CDLL:
         h.oracle_bf16_to_f32.restype = None
         h.oracle_bf16_to_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_int64]
         h.oracle_max_threads.restype = C.c_int
+        h.oracle_gemv_add.restype = C.c_int
+        h.oracle_gemv_add.argtypes = [C.c_void_p] * 4 + [C.c_int] * 3 + [C.c_int64, C.c_int]
+        h.oracle_qkv_gemv.restype = C.c_int
+        h.oracle_qkv_gemv.argtypes = [C.c_void_p] * 5 + [C.c_int] * 5
         _lib = h
     return _lib
 
@@ -171,3 +180,41 @@ def sin_cos_cache(head_dim: int, max_seq_len: int, form: int = 1):
     if rc != 0:
         raise ValueError("oracle_sin_cos_cache rejected its arguments")
     return s, c
+
+
+def gemv_add(x_bits: np.ndarray, w_bits: np.ndarray, residual_bits: np.ndarray, *, accum: int = 1,
+             k: Optional[int] = None):
+    """Output projection with residual add. x [batch, k] or [k], weight [n, ld >= k],
+    residual [batch, n] or [n], BF16 bits. accum 0: the reference kernel's FP32 order,
+    1: FP64 dot products, both rounded to BF16 bits; 2: the FP64 sums, not rounded."""
+    x = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    w = np.ascontiguousarray(w_bits, dtype=np.uint16)
+    r = np.array(residual_bits, dtype=np.uint16, copy=True)
+    x2 = x.reshape(-1, x.shape[-1])
+    batch, kk = x2.shape[0], (k if k is not None else x2.shape[1])
+    n, ld = w.shape
+    out64 = np.zeros((batch, n), dtype=np.float64)
+    rc = lib().oracle_gemv_add(x2.ctypes.data, w.ctypes.data, r.ctypes.data, out64.ctypes.data,
+                               batch, n, kk, ld, accum)
+    if rc != 0:
+        raise ValueError("oracle_gemv_add rejected its arguments")
+    return out64.reshape(r.shape) if accum == 2 else r
+
+
+def qkv_gemv(x_bits: np.ndarray, w_bits: np.ndarray, dim: int, kv_dim: int, *, accum: int = 1):
+    """Packed QKV projection. x [batch, hidden] or [hidden]; weight [dim + 2 kv_dim, hidden].
+    Returns (query, key, value) BF16 bits with x's leading shape."""
+    x = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    w = np.ascontiguousarray(w_bits, dtype=np.uint16)
+    x2 = x.reshape(-1, x.shape[-1])
+    batch, hidden = x2.shape
+    assert w.shape == (dim + 2 * kv_dim, hidden)
+    q = np.zeros((batch, dim), dtype=np.uint16)
+    k = np.zeros((batch, kv_dim), dtype=np.uint16)
+    v = np.zeros((batch, kv_dim), dtype=np.uint16)
+    rc = lib().oracle_qkv_gemv(x2.ctypes.data, w.ctypes.data, q.ctypes.data, k.ctypes.data,
+                               v.ctypes.data, batch, hidden, dim, kv_dim, accum)
+    if rc != 0:
+        raise ValueError("oracle_qkv_gemv rejected its arguments")
+    lead = x.shape[:-1]
+    return q.reshape(lead + (dim,)), k.reshape(lead + (kv_dim,)), v.reshape(lead + (kv_dim,))

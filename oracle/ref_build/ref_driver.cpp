@@ -9,6 +9,8 @@
 //   kernel::mha_kernel_cu                  code/source/op/kernel/cuda/mha_kernel.cu:440
 //   kernel::fused_qk_norm_rope_kernel_cu   code/source/op/kernel/cuda/rmsnorm_kernel.cu:257
 //   kernel::sin_cos_cache_precompute_cu    code/source/op/kernel/cuda/rope_kernel.cu:23
+//   kernel::fused_gemv_add_kernel_cu       code/source/op/kernel/cuda/matmul_kernel.cu:172
+//   kernel::fused_qkv_gemv_kernel_cu       code/source/op/kernel/cuda/matmul_kernel.cu:247
 #include <cstdint>
 #include <cuda_runtime.h>
 #include <utility>
@@ -28,6 +30,11 @@ void fused_qk_norm_rope_kernel_cu(const tensor::Tensor& query, const tensor::Ten
                                   int32_t dim, int32_t kv_dim, int32_t head_dim, void* stream);
 void sin_cos_cache_precompute_cu(const tensor::Tensor& sin_cache, const tensor::Tensor& cos_cache,
                                  int32_t head_dim, int32_t max_seq_len, void* stream);
+void fused_gemv_add_kernel_cu(const tensor::Tensor& input, const tensor::Tensor& weight,
+                              const tensor::Tensor& output, void* stream);
+void fused_qkv_gemv_kernel_cu(const tensor::Tensor& input, const tensor::Tensor& weight,
+                              const tensor::Tensor& query, const tensor::Tensor& key,
+                              const tensor::Tensor& value, void* stream);
 }  // namespace kernel
 
 namespace {
@@ -99,6 +106,32 @@ int ref_sin_cos_cache(void* sin_cache, void* cos_cache, int32_t head_dim, int32_
     tensor::Tensor s = borrow(fp32, {max_seq_len, head_dim / 2}, sin_cache, cuda);
     tensor::Tensor c = borrow(fp32, {max_seq_len, head_dim / 2}, cos_cache, cuda);
     kernel::sin_cos_cache_precompute_cu(s, c, head_dim, max_seq_len, stream);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// residual[n] = bf16(residual[n] + sum_k input[k] * weight[n, k]); all bf16 on the device.
+int ref_fused_gemv_add(void* input, void* weight, void* residual, int32_t n, int32_t k,
+                       void* stream) {
+    const auto cuda = base::DeviceType::DeviceCUDA;
+    const auto bf16 = base::DataType::DataTypeBf16;
+    tensor::Tensor in = borrow(bf16, {k}, input, cuda);
+    tensor::Tensor w = borrow(bf16, {n, k}, weight, cuda);
+    tensor::Tensor out = borrow(bf16, {n}, residual, cuda);
+    kernel::fused_gemv_add_kernel_cu(in, w, out, stream);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// weight [dim + 2 * kv_dim, hidden] -> query [dim], key [kv_dim], value [kv_dim]; all bf16.
+int ref_fused_qkv_gemv(void* input, void* weight, void* query, void* key, void* value,
+                       int32_t hidden, int32_t dim, int32_t kv_dim, void* stream) {
+    const auto cuda = base::DeviceType::DeviceCUDA;
+    const auto bf16 = base::DataType::DataTypeBf16;
+    tensor::Tensor in = borrow(bf16, {hidden}, input, cuda);
+    tensor::Tensor w = borrow(bf16, {dim + 2 * kv_dim, hidden}, weight, cuda);
+    tensor::Tensor q = borrow(bf16, {dim}, query, cuda);
+    tensor::Tensor k = borrow(bf16, {kv_dim}, key, cuda);
+    tensor::Tensor v = borrow(bf16, {kv_dim}, value, cuda);
+    kernel::fused_qkv_gemv_kernel_cu(in, w, q, k, v, stream);
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

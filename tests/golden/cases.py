@@ -35,6 +35,18 @@ FRONT_CASES = [
     ("pos12345", 32, 8, 12345),
     ("pos4095_group8", 64, 8, 4095),
 ]
+# Projections on either side of attention (single token, as the reference runs them).
+# name, output rows (hidden), input columns (query heads * 128)
+OPROJ_CASES = [
+    ("qwen3_0.6b", 1024, 2048),
+    ("qwen3_4b", 2560, 4096),
+    ("small", 48, 256),
+]
+# name, hidden, query heads, kv heads
+QKV_CASES = [
+    ("qwen3_0.6b", 1024, 16, 8),
+    ("qwen3_4b", 2560, 32, 8),
+]
 FRONT_TABLE_LEN = 16384
 TABLE_ROWS = [0, 1, 2, 5, 100, 1023, 4095, 12345, 16383]
 
@@ -79,6 +91,28 @@ def front_inputs(index: int):
     k = to_bf16_bits(rng.standard_normal((hkv, HEAD_DIM), dtype=np.float32))
     w = to_bf16_bits(1.0 + 0.05 * rng.standard_normal(2 * HEAD_DIM, dtype=np.float32))
     return q, k, w
+
+
+def oproj_inputs(index: int):
+    """Returns (x [k], weight [n, k], residual [n]) as BF16 bits: x, residual ~ N(0, 1),
+    weight ~ N(0, 1) / sqrt(k) so that the product is of unit scale."""
+    _, n, k = OPROJ_CASES[index]
+    rng = _rng(3, index)
+    x = to_bf16_bits(rng.standard_normal(k, dtype=np.float32))
+    w = to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32) / np.float32(np.sqrt(k)))
+    r = to_bf16_bits(rng.standard_normal(n, dtype=np.float32))
+    return x, w, r
+
+
+def qkv_inputs(index: int):
+    """Returns (x [hidden], weight [(hq + 2 hkv) * 128, hidden]) as BF16 bits."""
+    _, hidden, hq, hkv = QKV_CASES[index]
+    rng = _rng(4, index)
+    rows = (hq + 2 * hkv) * HEAD_DIM
+    x = to_bf16_bits(rng.standard_normal(hidden, dtype=np.float32))
+    w = to_bf16_bits(rng.standard_normal((rows, hidden), dtype=np.float32)
+                     / np.float32(np.sqrt(hidden)))
+    return x, w
 
 
 def checksum(*arrays: np.ndarray) -> int:

@@ -1,4 +1,6 @@
-"""Generates tests/golden/ref_cuda_bf16.npz from the reference's own CUDA kernels.
+"""Generates tests/golden/ref_cuda_bf16.npz (attention, front stage, tables) and
+tests/golden/ref_cuda_proj.npz (the projection GEMVs on either side of attention) from the
+reference's own CUDA kernels.
 
 Runs on a machine with a GPU and oracle/_ref/libref_attn.so (built beforehand by
 oracle/build_ref.sh from the reference checkout; the checkout itself is not needed at run
@@ -7,7 +9,7 @@ kernel::mha_kernel_cu / fused_qk_norm_rope_kernel_cu / sin_cos_cache_precompute_
 their outputs, together with a checksum of the inputs so that a drifting random generator is
 noticed. The oracle and the CUDA kernels of this repository are then tested against the file.
 
-usage: python tests/golden/make_golden.py [output.npz]
+usage: python tests/golden/make_golden.py [attn|proj|all]
 """
 from __future__ import annotations
 
@@ -25,9 +27,54 @@ import cases  # noqa: E402
 REF = HERE.parent.parent / "oracle" / "_ref" / "libref_attn.so"
 
 
+def up(bits: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(bits.view(np.int16)).to("cuda:0").view(torch.bfloat16)
+
+
+def down(t: torch.Tensor) -> np.ndarray:
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def projections(ref) -> None:
+    """kernel::fused_gemv_add_kernel_cu and kernel::fused_qkv_gemv_kernel_cu outputs."""
+    ref.ref_fused_gemv_add.restype = C.c_int
+    ref.ref_fused_gemv_add.argtypes = [C.c_void_p] * 3 + [C.c_int32] * 2 + [C.c_void_p]
+    ref.ref_fused_qkv_gemv.restype = C.c_int
+    ref.ref_fused_qkv_gemv.argtypes = [C.c_void_p] * 5 + [C.c_int32] * 3 + [C.c_void_p]
+    store = {}
+    for i, (name, n, k) in enumerate(cases.OPROJ_CASES):
+        x, w, r = cases.oproj_inputs(i)
+        dx, dw, dr = up(x), up(w), up(r).clone()
+        rc = ref.ref_fused_gemv_add(dx.data_ptr(), dw.data_ptr(), dr.data_ptr(), n, k, None)
+        torch.cuda.synchronize()
+        assert rc == 0, (name, rc)
+        store[f"oproj/{name}/out"] = down(dr)
+        store[f"oproj/{name}/crc"] = np.array([cases.checksum(x, w, r)], dtype=np.uint64)
+    for i, (name, hidden, hq, hkv) in enumerate(cases.QKV_CASES):
+        x, w = cases.qkv_inputs(i)
+        dim, kv_dim = hq * cases.HEAD_DIM, hkv * cases.HEAD_DIM
+        dx, dw = up(x), up(w)
+        q = torch.zeros(dim, dtype=torch.bfloat16, device="cuda:0")
+        k = torch.zeros(kv_dim, dtype=torch.bfloat16, device="cuda:0")
+        v = torch.zeros(kv_dim, dtype=torch.bfloat16, device="cuda:0")
+        rc = ref.ref_fused_qkv_gemv(dx.data_ptr(), dw.data_ptr(), q.data_ptr(), k.data_ptr(),
+                                    v.data_ptr(), hidden, dim, kv_dim, None)
+        torch.cuda.synchronize()
+        assert rc == 0, (name, rc)
+        store[f"qkv/{name}/q"], store[f"qkv/{name}/k"], store[f"qkv/{name}/v"] = down(q), down(k), down(v)
+        store[f"qkv/{name}/crc"] = np.array([cases.checksum(x, w)], dtype=np.uint64)
+    np.savez_compressed(HERE / "ref_cuda_proj.npz", **store)
+    print("wrote", HERE / "ref_cuda_proj.npz", "with", len(store), "arrays")
+
+
 def main() -> None:
-    out_path = Path(sys.argv[1]) if len(sys.argv) > 1 else HERE / "ref_cuda_bf16.npz"
+    what = sys.argv[1] if len(sys.argv) > 1 else "all"
     ref = C.CDLL(str(REF))
+    if what in ("proj", "all"):
+        projections(ref)
+    if what == "proj":
+        return
+    out_path = HERE / "ref_cuda_bf16.npz"
     ref.ref_mha_bf16.restype = C.c_int
     ref.ref_mha_bf16.argtypes = [C.c_void_p] * 4 + [C.c_int64, C.c_void_p] + [C.c_int32] * 8 + [C.c_void_p]
     ref.ref_fused_qk_norm_rope.restype = C.c_int
@@ -36,12 +83,6 @@ def main() -> None:
     ref.ref_sin_cos_cache.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
     dev = torch.device("cuda:0")
     store = {}
-
-    def up(bits: np.ndarray) -> torch.Tensor:
-        return torch.from_numpy(bits.view(np.int16)).to(dev).view(torch.bfloat16)
-
-    def down(t: torch.Tensor) -> np.ndarray:
-        return t.view(torch.int16).cpu().numpy().view(np.uint16)
 
     for i, (name, hq, hkv, length, layers, layer_id, max_seq_len) in enumerate(cases.ATTN_CASES):
         q, k, v = cases.attention_inputs(i)

@@ -3,6 +3,9 @@ reference-signature entry point) and against the golden outputs of the reference
 kernels (tests/golden/ref_cuda_bf16.npz)."""
 import numpy as np
 import pytest
+from pathlib import Path
+
+import helpers as H
 
 import cases
 from oracle import oracle
@@ -173,3 +176,58 @@ def test_oracle_against_reference_cuda_table(golden):
     tol = 2e-6 + 4 * np.spacing(np.maximum(theta, 1.0).astype(np.float32))
     assert np.all(np.abs(s1[rows] - golden["table/sin_rows"]) <= tol)
     assert np.all(np.abs(c1[rows] - golden["table/cos_rows"]) <= tol)
+
+
+# ---- projections on either side of attention ------------------------------------------------
+@pytest.fixture(scope="module")
+def golden_proj():
+    return np.load(Path(__file__).resolve().parent / "golden" / "ref_cuda_proj.npz")
+
+
+@pytest.mark.parametrize("index", range(len(cases.OPROJ_CASES)))
+def test_oproj_oracle_is_bit_equal_to_reference_kernel(golden_proj, index):
+    """The FP32 restatement follows the reference kernel's summation order exactly, so it
+    reproduces the output of kernel::fused_gemv_add_kernel_cu bit for bit."""
+    name, n, k = cases.OPROJ_CASES[index]
+    x, w, r = cases.oproj_inputs(index)
+    assert int(golden_proj[f"oproj/{name}/crc"][0]) == cases.checksum(x, w, r)
+    want = golden_proj[f"oproj/{name}/out"]
+    assert np.array_equal(oracle.gemv_add(x, w, r, accum=0), want)
+    # FP64 accumulation moves a result only across a BF16 rounding boundary.
+    got64 = oracle.gemv_add(x, w, r, accum=1)
+    assert H.bf16_ulp_distance(got64, want).max() <= 1
+    assert (got64 != want).mean() <= 0.01
+
+
+@pytest.mark.parametrize("index", range(len(cases.QKV_CASES)))
+def test_qkv_oracle_is_bit_equal_to_reference_kernel(golden_proj, index):
+    name, hidden, hq, hkv = cases.QKV_CASES[index]
+    x, w = cases.qkv_inputs(index)
+    assert int(golden_proj[f"qkv/{name}/crc"][0]) == cases.checksum(x, w)
+    got = oracle.qkv_gemv(x, w, hq * cases.HEAD_DIM, hkv * cases.HEAD_DIM, accum=0)
+    for part, bits in zip("qkv", got):
+        assert np.array_equal(bits, golden_proj[f"qkv/{name}/{part}"]), part
+    got64 = oracle.qkv_gemv(x, w, hq * cases.HEAD_DIM, hkv * cases.HEAD_DIM, accum=1)
+    for part, bits in zip("qkv", got64):
+        assert H.bf16_ulp_distance(bits, golden_proj[f"qkv/{name}/{part}"]).max() <= 1
+
+
+def test_gemv_add_batched_pitch_and_linearity():
+    """Batch rows are independent, a weight pitch larger than k reads only k columns, and the
+    unrounded FP64 result is linear in x."""
+    rng = np.random.default_rng(77)
+    n, k, ld = 32, 256, 384
+    x = cases.to_bf16_bits(rng.standard_normal((3, k), dtype=np.float32))
+    w = cases.to_bf16_bits(rng.standard_normal((n, ld), dtype=np.float32))
+    r = cases.to_bf16_bits(rng.standard_normal((3, n), dtype=np.float32))
+    whole = oracle.gemv_add(x, w, r, accum=0, k=k)
+    for b in range(3):
+        one = oracle.gemv_add(x[b], np.ascontiguousarray(w[:, :k]), r[b], accum=0)
+        assert np.array_equal(whole[b], one)
+    zero_r = np.zeros_like(r)
+    full = oracle.gemv_add(x, w, zero_r, accum=2, k=k)
+    xf = cases.bf16_bits_to_f32(x).astype(np.float64)
+    wf = cases.bf16_bits_to_f32(w[:, :k]).astype(np.float64)
+    assert np.allclose(full, xf @ wf.T, rtol=1e-12, atol=1e-12)
+    with pytest.raises(ValueError):
+        oracle.gemv_add(x[:, :12], w, r, accum=0)  # k % 8 != 0
