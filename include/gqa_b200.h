@@ -355,9 +355,50 @@ void gqa_comm_destroy(gqa_comm* comm);
  * local caches) and gathers every rank's output over NVLink on p->stream: with the peer-store
  * kernel when gqa_comm_enable_peer_gather was called and the output fits, else with one
  * ncclAllGather. p->out is the local output [batch, local_q_heads, head_dim]; gathered is
- * [nranks, batch, local_q_heads, head_dim].
+ * [nranks, batch, local_q_heads, head_dim]. When units are split and the combine grid
+ * (batch * local_q_heads CTAs) fits the GPU at once, the peer stores are issued by the combine
+ * kernel itself, row by row as rows are merged, and no separate gather kernel is launched.
  */
 int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathered);
+
+/* ---- the projection behind attention ---------------------------------------------------- */
+
+/*
+ * Output projection with residual add, the step that follows attention in a decoder layer:
+ *     residual[b, n] = bf16(float(residual[b, n]) + sum_c attn_out[b, c] * weight[n, c])
+ * Replaces kernel::fused_gemv_add_kernel_cu (code/source/op/kernel/cuda/matmul_kernel.cu:
+ * 143-208; single token there, `batch` tokens here, the weights are read once for all of
+ * them). FP32 accumulation on tensor cores; the summation order is fixed: columns are summed
+ * per query head, heads in ascending order per KV head, KV heads in ascending order. Results
+ * agree with the reference kernel to one BF16 unit in the last place.
+ *
+ * In a KV-head-parallel node every rank holds the columns of its own heads
+ * (gqa_oproj_residual_sharded): `weight` then points at this rank's first column inside the
+ * full matrix (weight_ld = the full row length) or at a packed slice (weight_ld = local
+ * columns), attn_out is the rank's LOCAL attention output (no gather of it is needed), and
+ * the per-KV-head partial sums are exchanged through the peer windows of
+ * gqa_comm_enable_peer_gather (which must have been called with max_bytes_per_rank >=
+ * 4 * local_kv_heads * min(batch, 8) * hidden). Every rank ends with the same, complete
+ * `residual`, bit-equal to what the unsharded call computes. A wait that runs out sets
+ * *status_dev to 2.
+ */
+typedef struct gqa_oproj_params {
+    int32_t batch;        /* tokens (sequences of a decode step) */
+    int32_t hidden;       /* output rows; a multiple of 16 */
+    int32_t num_q_heads;  /* query heads whose columns this call holds: 1, 2, 4 or 8 * j */
+    int32_t num_kv_heads; /* KV heads they belong to; divides num_q_heads */
+    int32_t head_dim;     /* 128 */
+    int32_t reserved;
+    int64_t weight_ld;    /* elements between weight rows, >= num_q_heads * 128, % 8 == 0 */
+    const void* attn_out; /* [batch, num_q_heads * 128] bf16 */
+    const void* weight;   /* bf16, row n column c at weight[n * weight_ld + c] */
+    void* residual;       /* [batch, hidden] bf16, read and written */
+    int32_t* status_dev;  /* may be null */
+    void* stream;
+} gqa_oproj_params;
+
+int gqa_oproj_residual(const gqa_oproj_params* p);
+int gqa_oproj_residual_sharded(const gqa_oproj_params* p, gqa_comm* comm);
 
 #ifdef __cplusplus
 }

@@ -17,6 +17,7 @@ from .binding import (  # noqa: F401
     layout_pool,
     layout_reference,
     lib,
+    oproj_residual,
     qk_norm_rope_append,
     shard_plan,
     sin_cos_cache,

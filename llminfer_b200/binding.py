@@ -106,6 +106,23 @@ class _FrontParams(C.Structure):
 
 
 # Every symbol include/gqa_b200.h declares, with its ctypes signature.
+class _OprojParams(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32),
+        ("hidden", C.c_int32),
+        ("num_q_heads", C.c_int32),
+        ("num_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("reserved", C.c_int32),
+        ("weight_ld", C.c_int64),
+        ("attn_out", C.c_void_p),
+        ("weight", C.c_void_p),
+        ("residual", C.c_void_p),
+        ("status_dev", C.c_void_p),
+        ("stream", C.c_void_p),
+    ]
+
+
 _SIGNATURES = {
     "gqa_status_string": (C.c_char_p, [C.c_int]),
     "gqa_abi_version": (C.c_int, []),
@@ -146,6 +163,8 @@ _SIGNATURES = {
     "gqa_comm_init": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
     "gqa_comm_destroy": (None, [C.c_void_p]),
     "gqa_decode_sharded": (C.c_int, [C.POINTER(_DecodeParams), C.c_void_p, C.c_void_p]),
+    "gqa_oproj_residual": (C.c_int, [C.POINTER(_OprojParams)]),
+    "gqa_oproj_residual_sharded": (C.c_int, [C.POINTER(_OprojParams), C.c_void_p]),
 }
 
 _lib: Optional[C.CDLL] = None
@@ -530,3 +549,28 @@ def decode_sharded(comm: ShardComm, gathered: torch.Tensor, q, k_cache, v_cache,
                        kw.get("plan_len_hint", 0), kw.get("status"), stream, keep,
                        kw.get("early_prefetch", False))
     _check(lib().gqa_decode_sharded(C.byref(p), comm._h, _ptr(gathered)), "gqa_decode_sharded")
+
+
+def oproj_residual(attn_out: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, *,
+                   num_kv_heads: int, comm: Optional[ShardComm] = None,
+                   weight_ld: Optional[int] = None, status: Optional[torch.Tensor] = None,
+                   stream: Optional[int] = None) -> None:
+    """residual [batch, hidden] += attn_out [batch, heads, 128] . weight[hidden, heads * 128]^T.
+
+    `weight` may be a column slice of a wider matrix: pass the slice's first element as a
+    tensor view and the full row length as `weight_ld`. With `comm` the per-KV-head sums are
+    exchanged over the peer windows and every rank ends with the complete result."""
+    batch, heads, dim = attn_out.shape
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    p = _OprojParams()
+    p.batch, p.hidden = batch, residual.shape[-1]
+    p.num_q_heads, p.num_kv_heads, p.head_dim = heads, num_kv_heads, dim
+    p.weight_ld = weight_ld if weight_ld is not None else weight.stride(0)
+    p.attn_out, p.weight, p.residual = _ptr(attn_out), _ptr(weight), _ptr(residual)
+    p.status_dev, p.stream = _ptr(status), stream
+    if comm is None:
+        _check(lib().gqa_oproj_residual(C.byref(p)), "gqa_oproj_residual")
+    else:
+        _check(lib().gqa_oproj_residual_sharded(C.byref(p), comm._h),
+               "gqa_oproj_residual_sharded")

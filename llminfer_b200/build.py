@@ -28,6 +28,7 @@ KERNEL_SOURCES = [
     "csrc/static_scratch.cu",
     "csrc/kv_pool.cpp",
     "csrc/shard_comm.cu",
+    "csrc/proj.cu",
 ]
 KERNEL_HEADERS = ["csrc/ptx.cuh", "csrc/work_map.cuh", "csrc/decode_kernels.cuh",
                   "csrc/peer_window.cuh"]

@@ -9,7 +9,10 @@
 // word that shows the current step has arrived. No fences, no separate flags.
 #pragma once
 
+#include <cstddef>
 #include <cstdint>
+
+struct gqa_comm;
 
 namespace gqa {
 
@@ -34,6 +37,12 @@ struct PeerGatherArgs {
     int32_t nranks;
     int32_t rank;
 };
+
+// Host side: the windows of a communicator for an exchange of `bytes_per_rank` payload bytes
+// per rank. GQA_ERR_COMM when the peer windows were not set up, GQA_ERR_SHAPE when a slot is
+// too small for that payload.
+int comm_peer_args(const gqa_comm* comm, size_t bytes_per_rank, int32_t* status_dev,
+                   PeerGatherArgs* out);
 
 __device__ __forceinline__ WindowCtrl* window_ctrl(uint8_t* window, uint64_t slot_bytes,
                                                    int nranks) {

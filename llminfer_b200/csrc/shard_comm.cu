@@ -174,6 +174,15 @@ PeerGatherArgs gather_args(const gqa_comm* comm, const void* send, void* recv, s
 
 }  // namespace
 
+int gqa::comm_peer_args(const gqa_comm* comm, size_t bytes_per_rank, int32_t* status_dev,
+                        PeerGatherArgs* out) {
+    if (comm == nullptr || out == nullptr) return GQA_ERR_NULL;
+    if (comm->window_local == nullptr) return GQA_ERR_COMM;
+    if (bytes_per_rank == 0 || 2 * bytes_per_rank > comm->slot_bytes) return GQA_ERR_SHAPE;
+    *out = gather_args(comm, nullptr, nullptr, bytes_per_rank, status_dev);
+    return GQA_OK;
+}
+
 extern "C" {
 
 int gqa_shard_plan(int32_t num_q_heads, int32_t num_kv_heads, int32_t nranks, int32_t rank,

@@ -1,0 +1,122 @@
+"""GPU parity of the output projection with residual add (gqa_oproj_residual) against the
+golden outputs of the reference's own kernel and against the CPU oracle."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+import helpers as H
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+ULP_TOL = 1            # BF16 units in the last place, against the reference kernel's output
+MISMATCH_TOL = 0.02    # share of outputs allowed to sit on the other side of a rounding boundary
+
+
+@pytest.fixture(scope="module")
+def gqa(built_lib):
+    import llminfer_b200
+    return llminfer_b200
+
+
+@pytest.fixture(scope="module")
+def golden_proj():
+    return np.load(Path(__file__).resolve().parent / "golden" / "ref_cuda_proj.npz")
+
+
+def run(gqa, x_bits, w_bits, r_bits, *, kv_heads, **kw):
+    """x [batch, k], w [n, ld], r [batch, n] bits -> new residual bits."""
+    batch, k = x_bits.shape
+    x = H.bf16_tensor(x_bits).reshape(batch, k // 128, 128)
+    w = H.bf16_tensor(w_bits)
+    r = H.bf16_tensor(r_bits).clone()
+    gqa.oproj_residual(x, w, r, num_kv_heads=kv_heads, **kw)
+    torch.cuda.synchronize()
+    return H.bits_of(r)
+
+
+def check(got, want, where):
+    dist = H.bf16_ulp_distance(got, want)
+    assert dist.max() <= ULP_TOL, (where, int(dist.max()))
+    assert (got != want).mean() <= MISMATCH_TOL, (where, float((got != want).mean()))
+
+
+@pytest.mark.parametrize("index", range(len(cases.OPROJ_CASES)))
+def test_matches_reference_kernel_output(gqa, golden_proj, index):
+    name, n, k = cases.OPROJ_CASES[index]
+    x, w, r = cases.oproj_inputs(index)
+    heads = k // 128
+    for kv_heads in sorted({1, min(heads, 2), min(heads, 8)}):
+        got = run(gqa, x[None], w, r[None], kv_heads=kv_heads)[0]
+        check(got, golden_proj[f"oproj/{name}/out"], (name, kv_heads, "reference kernel"))
+        check(got, oracle.gemv_add(x, w, r, accum=1), (name, kv_heads, "fp64 oracle"))
+
+
+@pytest.mark.parametrize("batch", [1, 3, 8, 11])
+@pytest.mark.parametrize("heads,kv_heads", [(1, 1), (2, 1), (4, 2), (8, 8), (16, 8), (40, 8)])
+def test_batches_and_head_counts(gqa, batch, heads, kv_heads):
+    rng = np.random.default_rng(1000 * batch + heads)
+    n, k = 80, heads * 128
+    x = cases.to_bf16_bits(rng.standard_normal((batch, k), dtype=np.float32))
+    w = cases.to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32) / np.float32(np.sqrt(k)))
+    r = cases.to_bf16_bits(rng.standard_normal((batch, n), dtype=np.float32))
+    got = run(gqa, x, w, r, kv_heads=kv_heads)
+    check(got, oracle.gemv_add(x, w, r, accum=1), "fp64 oracle")
+    # A token's result does not depend on which other tokens share the launch.
+    for b in (0, batch - 1):
+        alone = run(gqa, x[b:b + 1], w, r[b:b + 1], kv_heads=kv_heads)
+        assert np.array_equal(alone[0], got[b])
+
+
+def test_column_slice_of_a_wider_matrix(gqa):
+    """Each rank of a KV-head-parallel node reads its own columns inside the full matrix."""
+    rng = np.random.default_rng(5)
+    n, heads, total_heads = 64, 8, 32
+    k, ld = heads * 128, total_heads * 128
+    x = cases.to_bf16_bits(rng.standard_normal((2, k), dtype=np.float32))
+    w_full = cases.to_bf16_bits(rng.standard_normal((n, ld), dtype=np.float32) / np.float32(32.0))
+    r = cases.to_bf16_bits(rng.standard_normal((2, n), dtype=np.float32))
+    first = 16 * 128
+    packed = np.ascontiguousarray(w_full[:, first:first + k])
+    want = run(gqa, x, packed, r, kv_heads=2)
+    w_dev = H.bf16_tensor(w_full)
+    res = H.bf16_tensor(r).clone()
+    gqa.oproj_residual(H.bf16_tensor(x).reshape(2, heads, 128), w_dev[:, first:], res, num_kv_heads=2)
+    torch.cuda.synchronize()
+    assert np.array_equal(H.bits_of(res), want)
+    check(want, oracle.gemv_add(x, packed, r, accum=1), "fp64 oracle")
+
+
+def test_qwen3_32b_shape_batch4(gqa):
+    """The benchmark model's projection: 5120 rows, 64 heads, 4 tokens."""
+    rng = np.random.default_rng(32)
+    n, heads, batch = 5120, 64, 4
+    k = heads * 128
+    x = cases.to_bf16_bits(rng.standard_normal((batch, k), dtype=np.float32))
+    w = cases.to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32) / np.float32(np.sqrt(k)))
+    r = cases.to_bf16_bits(rng.standard_normal((batch, n), dtype=np.float32))
+    got = run(gqa, x, w, r, kv_heads=8)
+    check(got, oracle.gemv_add(x, w, r, accum=1), "fp64 oracle")
+    # Linearity in the residual: a zero residual gives the bare product, rounded once.
+    bare = run(gqa, x, w, np.zeros_like(r), kv_heads=8)
+    full = oracle.gemv_add(x, w, np.zeros_like(r), accum=2)
+    check(bare, cases.to_bf16_bits(full.astype(np.float32)), "bare product")
+
+
+def test_rejects_unsupported_shapes(gqa):
+    x = torch.zeros(1, 8, 128, dtype=torch.bfloat16, device="cuda:0")
+    w = torch.zeros(64, 1024, dtype=torch.bfloat16, device="cuda:0")
+    r = torch.zeros(1, 64, dtype=torch.bfloat16, device="cuda:0")
+    with pytest.raises(gqa.GqaError):
+        gqa.oproj_residual(x, w, r[:, :56], num_kv_heads=8)       # rows not a multiple of 16
+    with pytest.raises(gqa.GqaError):
+        gqa.oproj_residual(x, w, r, num_kv_heads=3)               # heads not divisible
+    with pytest.raises(gqa.GqaError):
+        gqa.oproj_residual(x[:, :3], w, r, num_kv_heads=1)        # 3 heads: no warp layout
+    with pytest.raises(gqa.GqaError):
+        gqa.oproj_residual(x, w, r, num_kv_heads=8, weight_ld=512)  # pitch below the columns
+    with pytest.raises(gqa.GqaError):
+        gqa.oproj_residual(x, w.view(-1)[4:4 + 64 * 1016].view(64, 1016), r, num_kv_heads=8)
