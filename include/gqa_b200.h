@@ -385,17 +385,28 @@ int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathere
 typedef struct gqa_oproj_params {
     int32_t batch;        /* tokens (sequences of a decode step) */
     int32_t hidden;       /* output rows; a multiple of 16 */
-    int32_t num_q_heads;  /* query heads whose columns this call holds: 1, 2, 4 or 8 * j */
-    int32_t num_kv_heads; /* KV heads they belong to; divides num_q_heads */
+    int32_t num_q_heads;  /* query heads whose columns this call holds */
+    int32_t num_kv_heads; /* KV heads they belong to: divides num_q_heads, quotient <= 16 */
     int32_t head_dim;     /* 128 */
     int32_t reserved;
     int64_t weight_ld;    /* elements between weight rows, >= num_q_heads * 128, % 8 == 0 */
     const void* attn_out; /* [batch, num_q_heads * 128] bf16 */
     const void* weight;   /* bf16, row n column c at weight[n * weight_ld + c] */
     void* residual;       /* [batch, hidden] bf16, read and written */
+    void* workspace;      /* gqa_oproj_workspace_bytes() bytes, 16-byte aligned; null if 0 */
+    size_t workspace_bytes;
     int32_t* status_dev;  /* may be null */
     void* stream;
 } gqa_oproj_params;
+
+/*
+ * Workspace of the projection for `num_kv_heads` KV heads held by the caller (0 for one KV
+ * head). The caller zero-fills it once after allocating it; every call leaves it zeroed
+ * where that matters (per-tile arrival counters), so it can be reused by the next call on
+ * the same stream without further care. Calls that overlap on different streams need
+ * workspaces of their own.
+ */
+size_t gqa_oproj_workspace_bytes(int32_t hidden, int32_t num_kv_heads);
 
 int gqa_oproj_residual(const gqa_oproj_params* p);
 int gqa_oproj_residual_sharded(const gqa_oproj_params* p, gqa_comm* comm);

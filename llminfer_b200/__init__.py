@@ -18,6 +18,7 @@ from .binding import (  # noqa: F401
     layout_reference,
     lib,
     oproj_residual,
+    oproj_workspace,
     qk_norm_rope_append,
     shard_plan,
     sin_cos_cache,

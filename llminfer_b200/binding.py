@@ -118,6 +118,8 @@ class _OprojParams(C.Structure):
         ("attn_out", C.c_void_p),
         ("weight", C.c_void_p),
         ("residual", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
         ("status_dev", C.c_void_p),
         ("stream", C.c_void_p),
     ]
@@ -163,6 +165,7 @@ _SIGNATURES = {
     "gqa_comm_init": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
     "gqa_comm_destroy": (None, [C.c_void_p]),
     "gqa_decode_sharded": (C.c_int, [C.POINTER(_DecodeParams), C.c_void_p, C.c_void_p]),
+    "gqa_oproj_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "gqa_oproj_residual": (C.c_int, [C.POINTER(_OprojParams)]),
     "gqa_oproj_residual_sharded": (C.c_int, [C.POINTER(_OprojParams), C.c_void_p]),
 }
@@ -551,15 +554,24 @@ def decode_sharded(comm: ShardComm, gathered: torch.Tensor, q, k_cache, v_cache,
     _check(lib().gqa_decode_sharded(C.byref(p), comm._h, _ptr(gathered)), "gqa_decode_sharded")
 
 
+def oproj_workspace(hidden: int, num_kv_heads: int, device) -> Optional[torch.Tensor]:
+    """Zero-filled workspace for oproj_residual (None when none is needed)."""
+    nbytes = lib().gqa_oproj_workspace_bytes(hidden, num_kv_heads)
+    if nbytes == 0:
+        return None
+    return torch.zeros(nbytes, dtype=torch.uint8, device=device)
+
+
 def oproj_residual(attn_out: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, *,
-                   num_kv_heads: int, comm: Optional[ShardComm] = None,
-                   weight_ld: Optional[int] = None, status: Optional[torch.Tensor] = None,
+                   num_kv_heads: int, workspace: Optional[torch.Tensor] = None,
+                   comm: Optional[ShardComm] = None, weight_ld: Optional[int] = None, status: Optional[torch.Tensor] = None,
                    stream: Optional[int] = None) -> None:
     """residual [batch, hidden] += attn_out [batch, heads, 128] . weight[hidden, heads * 128]^T.
 
     `weight` may be a column slice of a wider matrix: pass the slice's first element as a
     tensor view and the full row length as `weight_ld`. With `comm` the per-KV-head sums are
-    exchanged over the peer windows and every rank ends with the complete result."""
+    exchanged over the peer windows and every rank ends with the complete result.
+    `workspace` comes from oproj_workspace() (needed for more than one KV head)."""
     batch, heads, dim = attn_out.shape
     if stream is None:
         stream = torch.cuda.current_stream().cuda_stream
@@ -569,6 +581,8 @@ def oproj_residual(attn_out: torch.Tensor, weight: torch.Tensor, residual: torch
     p.weight_ld = weight_ld if weight_ld is not None else weight.stride(0)
     p.attn_out, p.weight, p.residual = _ptr(attn_out), _ptr(weight), _ptr(residual)
     p.status_dev, p.stream = _ptr(status), stream
+    if workspace is not None:
+        p.workspace, p.workspace_bytes = _ptr(workspace), workspace.numel() * workspace.element_size()
     if comm is None:
         _check(lib().gqa_oproj_residual(C.byref(p)), "gqa_oproj_residual")
     else:

@@ -44,6 +44,11 @@ bool combine_can_gather(int batch, int num_q_heads, int sm_count);
 // tells whether it was (if not, nothing was exchanged and the caller gathers separately).
 int decode_with_gather(const gqa_decode_params* p, const PeerGatherArgs* gather, bool* fused);
 
+// Tensor map of a row-major BF16 matrix [rows][cols] with `pitch` elements between rows, boxes
+// of 16 rows x 64 columns in 128-byte swizzled rows (cached: weights keep their address).
+int cached_matrix_map(const void* base, int64_t cols, int64_t rows, int64_t pitch,
+                      CUtensorMap* map);
+
 struct FrontArgs {
     const void* q;
     void* q_out;

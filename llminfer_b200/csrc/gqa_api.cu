@@ -382,6 +382,50 @@ gqa_kv_layout clean_layout(const gqa_kv_layout& l) {
 
 }  // namespace
 
+int gqa::cached_matrix_map(const void* base, int64_t cols, int64_t rows, int64_t pitch,
+                           CUtensorMap* map) {
+    struct Entry {
+        const void* base;
+        int64_t cols, rows, pitch;
+        CUtensorMap map;
+    };
+    static std::mutex mu;
+    static std::vector<Entry> cache;
+    static size_t next = 0;
+    std::lock_guard<std::mutex> lock(mu);
+    for (const auto& e : cache) {
+        if (e.base == base && e.cols == cols && e.rows == rows && e.pitch == pitch) {
+            *map = e.map;
+            return GQA_OK;
+        }
+    }
+    auto fn = encode_fn();
+    if (fn == nullptr) return GQA_ERR_CUDA;
+    Entry e;
+    std::memset(&e, 0, sizeof(e));
+    e.base = base;
+    e.cols = cols;
+    e.rows = rows;
+    e.pitch = pitch;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
+    cuuint32_t box[2] = {64, 16};
+    cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(&e.map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
+                          dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return GQA_ERR_UNSUPPORTED;
+    if (cache.size() < 64) {
+        cache.push_back(e);
+    } else {
+        cache[next] = e;
+        next = (next + 1) % cache.size();
+    }
+    *map = e.map;
+    return GQA_OK;
+}
+
 extern "C" {
 
 const char* gqa_status_string(int status) {

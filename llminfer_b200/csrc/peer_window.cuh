@@ -61,6 +61,12 @@ __device__ __forceinline__ void push_word(unsigned long long* dst, uint32_t step
     asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(dst), "l"(word) : "memory");
 }
 
+__device__ __forceinline__ unsigned long long load_word(const unsigned long long* src) {
+    unsigned long long word;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(word) : "l"(src) : "memory");
+    return word;
+}
+
 // Polls one word until it shows `step` or the time limit passes (false).
 __device__ __forceinline__ bool poll_word(const unsigned long long* src, uint32_t step,
                                           unsigned long long start_ns, uint32_t* data) {

@@ -6,24 +6,33 @@
 // up to 8 tokens and multiplied on tensor cores: a warp owns 16 weight rows (the M side of
 // mma.m16n8k16), the tokens sit on the N side, accumulation is FP32.
 //
-// Fragments come straight from global memory, without a shared-memory stage: a dot product
-// does not care in which order its terms are added, so within a block of 32 columns thread
-// (g, t) of a warp loads the 8 consecutive columns 8t..8t+7 of rows g and g+8 with two 16-byte
-// loads, takes the same 8 columns of token g's activations, and feeds them to two MMAs as if
-// they were the columns the fragment layout expects. Both operands use the same permutation,
-// every column is used exactly once.
+// Work decomposition: a task is a (16-row tile, KV head) pair and belongs to one warp, which
+// multiplies the KV head's columns with 8 MMAs per query head into eight independent
+// accumulators. The weights arrive by TMA, one query head (16 x 128, 4 KiB, two
+// boxes of 64 columns in 128-byte swizzled rows) per stage of a ring that is private to the
+// warp; the warp refills a stage as soon as it has read it, so its loads run `stages` heads
+// ahead of the arithmetic. Warps never wait for one another while they stream: a CTA is a
+// bundle of up to four such warps that share one KV head, whose activations (up to 8 tokens)
+// sit in shared memory as the B operand. A fragments come from the ring with ldmatrix.
 //
 // Summation order (fixed, so that a KV-head-parallel node reproduces the single-GPU result
-// bit for bit): one partial per query head (128 columns, 8 MMAs from a zero accumulator),
-// heads added in ascending order per KV head, KV heads added in ascending order, then the
-// residual. A CTA of 8 warps covers 16 * tiles_per_cta rows and all local heads; head partials
-// meet in shared memory. In the sharded form every rank pushes its per-KV-head sums to the
-// peers' windows as step-tagged words (plain stores over NVLink) and polls, with a time
-// limit, for the sums of the KV heads it does not own.
+// bit for bit): per KV head eight FP32 accumulators, one per block of 16 columns inside a
+// query head, each running over the KV head's query heads in ascending order; the eight are
+// added in ascending order, KV heads are added in ascending order, then the residual.
+//
+// A KV head's sum is stored in a small workspace as an 8-byte word that carries the sum and
+// the launch number (so no fence or atomic is needed), and in the sharded form pushed to
+// every rank's window in the same format (plain stores over NVLink). When a CTA has streamed
+// all its tasks it finishes its share of the outputs: it polls (with a time limit) for the
+// words of all KV heads, adds them in ascending order and updates the residual.
 #include "../../include/gqa_b200.h"
 
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <mutex>
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -34,174 +43,281 @@
 namespace gqa {
 namespace {
 
-constexpr int kProjWarps = 8;
-constexpr int kProjThreads = kProjWarps * 32;
+constexpr int kProjMaxWarps = 4;
 constexpr int kProjTokens = 8;   // tokens per launch: the N side of the MMA
-constexpr int kTileRows = 16;    // weight rows per warp: the M side of the MMA
-constexpr int kTileOutputs = kTileRows * kProjTokens;
-constexpr int kMaxLocalGroups = 8;
+constexpr int kTileRows = 16;    // weight rows per task: the M side of the MMA
+constexpr int kMaxHeadsPerGroup = 16;
+constexpr int kHeadTileBytes = kTileRows * kHeadDim * 2;  // 4 KiB: one head of one tile
+constexpr int kBoxBytes = kHeadTileBytes / 2;
+constexpr uint64_t kProjWaitNs = 2000000000ull;
+constexpr int kMaxSmem = 224 * 1024;  // leaves room for the static part
 
 struct OprojArgs {
     const __nv_bfloat16* x;    // [batch][heads * 128]
-    const __nv_bfloat16* w;    // row n, column c at w[n * ld + c]
     __nv_bfloat16* residual;   // [batch][hidden]
-    int64_t ld;
+    WindowCtrl* ctrl;          // launch counter of the workspace (null for one KV head)
+    unsigned long long* words; // [groups][batch][hidden] tagged KV-head sums
+    int32_t* status;
     int32_t batch;             // <= 8
     int32_t hidden;
     int32_t heads;             // local query heads
-    int32_t groups;            // local KV heads
-    int32_t tiles_per_cta;
-    int32_t heads_per_warp;
+    int32_t groups;            // local KV heads; the grid is a multiple of it
+    int32_t stages;            // ring depth per warp
 };
 
+// Waits for a stage to fill; false when the time limit ran out. The clock is looked at only
+// now and then: reading it goes through the same queue as the loads and stores.
+__device__ __forceinline__ bool wait_full(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long start = 0;
+    for (uint32_t tries = 1;; ++tries) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((tries & 255u) == 0) {
+            const unsigned long long now = global_timer();
+            if (start == 0) start = now;
+            if (now - start > kProjWaitNs) return false;
+        }
+    }
+}
+
 template <bool SHARDED>
-__global__ void __launch_bounds__(kProjThreads, 3)
-    oproj_residual_kernel(const OprojArgs a, const PeerGatherArgs g) {
-    extern __shared__ float s_part[];  // [tiles_per_cta][heads][16 rows][8 tokens]
+__global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
+    oproj_residual_kernel(const __grid_constant__ CUtensorMap wmap, const OprojArgs a,
+                          const PeerGatherArgs g) {
+    // [warps][stages] head tiles (1 KiB aligned), then the KV head's activations
+    // [8 tokens][heads per KV head * 128 + 8] (rows padded by 16 bytes: conflict-free
+    // ldmatrix), then the stage barriers.
+    extern __shared__ uint8_t s_raw[];
+    uint8_t* s_dyn = reinterpret_cast<uint8_t*>(
+        (reinterpret_cast<uintptr_t>(s_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     __shared__ uint32_t s_step;
+    __shared__ uint32_t s_local_step;
     __shared__ int s_timed_out;
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int gid = lane >> 2;
-    const int tig = lane & 3;
-    const int warps_per_tile = kProjWarps / a.tiles_per_cta;
-    const int tile_in_cta = warp / warps_per_tile;
-    // Warp `sub` of a tile takes heads sub, sub + warps_per_tile, ...: at any moment the warps
-    // of a tile read neighbouring 256-byte pieces of the same weight rows.
-    const int sub = warp - tile_in_cta * warps_per_tile;
-    const int row0 = (blockIdx.x * a.tiles_per_cta + tile_in_cta) * kTileRows;
-    const bool active = row0 < a.hidden;
-    const int xcols = a.heads * kHeadDim;
+    const int nwarps = blockDim.x >> 5;
+    const int per_group = a.heads / a.groups;
+    const int tiles = a.hidden / kTileRows;
+    // CTA c works on KV head c % groups; the warps of all CTAs of a KV head share its tiles.
+    const int lg = blockIdx.x % a.groups;
+    const int worker = (blockIdx.x / a.groups) * nwarps + warp;
+    const int workers = (gridDim.x / a.groups) * nwarps;
+    const int x_pitch = per_group * kHeadDim * 2 + 16;  // bytes per token row
+    const uint32_t ring = smem_u32(s_dyn) + warp * a.stages * kHeadTileBytes;
+    uint8_t* s_x = s_dyn + nwarps * a.stages * kHeadTileBytes;
+    const uint32_t bars = smem_u32(s_x + kProjTokens * x_pitch) + warp * a.stages * 8;
 
-    uint4 wlo[4], whi[4];
-    const __nv_bfloat16* wrow = a.w + (int64_t)(row0 + gid) * a.ld + sub * kHeadDim + 8 * tig;
-    auto load_weights = [&](int hh) {
-        const __nv_bfloat16* p = wrow + (int64_t)hh * warps_per_tile * kHeadDim;
-#pragma unroll
-        for (int kb = 0; kb < 4; ++kb) {
-            wlo[kb] = __ldcs(reinterpret_cast<const uint4*>(p + 32 * kb));
-            whi[kb] = __ldcs(reinterpret_cast<const uint4*>(p + 8 * a.ld + 32 * kb));
+    // ---- producer side: the warp's sequence of (tile, head) stages ------------------------
+    const uint64_t policy = l2_policy_evict_first();
+    int prod_tile = worker, prod_head = 0, prod_stage = 0;
+    auto issue = [&]() {
+        if (prod_tile >= tiles) return;
+        if (lane == 0) {
+            const int col = (lg * per_group + prod_head) * kHeadDim;
+            const uint32_t bar = bars + prod_stage * 8;
+            const uint32_t dst = ring + prod_stage * kHeadTileBytes;
+            // No proxy fence: the stage was only read, and every lane's ldmatrix results had
+            // been consumed by its MMAs before the __syncwarp that precedes this call.
+            mbar_arrive_expect_tx(bar, kHeadTileBytes);
+            tma_load_2d(dst, &wmap, bar, col, prod_tile * kTileRows, policy);
+            tma_load_2d(dst + kBoxBytes, &wmap, bar, col + 64, prod_tile * kTileRows, policy);
+        }
+        if (++prod_stage == a.stages) prod_stage = 0;
+        if (++prod_head == per_group) {
+            prod_head = 0;
+            prod_tile += workers;
         }
     };
-    // The weights do not depend on the kernel in front: fetch the first head's before waiting.
-    if (active) load_weights(0);
-    pdl_wait();
-    if (SHARDED && threadIdx.x == 0) {
-        WindowCtrl* ctrl = window_ctrl(g.windows[g.rank], g.slot_bytes, g.nranks);
-        s_step = *reinterpret_cast<volatile uint32_t*>(&ctrl->step) + 1;
-        s_timed_out = 0;
+    if (lane == 0) {
+        prefetch_tensormap(&wmap);
+        for (int s = 0; s < a.stages; ++s) mbar_init(bars + s * 8, 1);
+        mbar_init_fence();
     }
-    if (active) {
-        for (int hh = 0; hh < a.heads_per_warp; ++hh) {
-            const int head = hh * warps_per_tile + sub;
-            uint4 xf[4];
-            if (gid < a.batch) {
-                const __nv_bfloat16* xp = a.x + (int64_t)gid * xcols + head * kHeadDim + 8 * tig;
-#pragma unroll
-                for (int kb = 0; kb < 4; ++kb) {
-                    xf[kb] = __ldcg(reinterpret_cast<const uint4*>(xp + 32 * kb));
-                }
-            } else {
-#pragma unroll
-                for (int kb = 0; kb < 4; ++kb) xf[kb] = make_uint4(0u, 0u, 0u, 0u);
+    __syncwarp();
+    // The weights do not depend on the kernel in front: fill the ring before waiting for it.
+    for (int s = 0; s < a.stages; ++s) issue();
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        s_timed_out = 0;
+        s_step = 0;
+        s_local_step = 0;
+        if (SHARDED) {
+            WindowCtrl* ctrl = window_ctrl(g.windows[g.rank], g.slot_bytes, g.nranks);
+            s_step = *reinterpret_cast<volatile uint32_t*>(&ctrl->step) + 1;
+        }
+        if (a.ctrl != nullptr) {
+            s_local_step = *reinterpret_cast<volatile uint32_t*>(&a.ctrl->step) + 1;
+        }
+    }
+    {
+        // The KV head's activations, tokens beyond the batch as zeros.
+        const int per_token = per_group * (kHeadDim / 8);
+        const int xcols = a.heads * kHeadDim;
+        for (int i = threadIdx.x; i < kProjTokens * per_token; i += blockDim.x) {
+            const int tok = i / per_token;
+            const int c = i - tok * per_token;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (tok < a.batch) {
+                v = __ldcg(reinterpret_cast<const uint4*>(a.x + (int64_t)tok * xcols +
+                                                          lg * per_group * kHeadDim) + c);
             }
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int kb = 0; kb < 4; ++kb) {
-                mma_bf16_16816(acc, wlo[kb].x, whi[kb].x, wlo[kb].y, whi[kb].y, xf[kb].x, xf[kb].y);
-                mma_bf16_16816(acc, wlo[kb].z, whi[kb].z, wlo[kb].w, whi[kb].w, xf[kb].z, xf[kb].w);
-            }
-            if (hh + 1 < a.heads_per_warp) load_weights(hh + 1);
-            float* dst = s_part + (int64_t)(tile_in_cta * a.heads + head) * kTileOutputs;
-            *reinterpret_cast<float2*>(dst + gid * kProjTokens + 2 * tig) =
-                make_float2(acc[0], acc[1]);
-            *reinterpret_cast<float2*>(dst + (gid + 8) * kProjTokens + 2 * tig) =
-                make_float2(acc[2], acc[3]);
+            *reinterpret_cast<uint4*>(s_x + tok * x_pitch + c * 16) = v;
         }
     }
     __syncthreads();
+    const uint32_t step = s_step;
+    const uint32_t local_step = s_local_step;
+    const int count = (SHARDED ? g.nranks : 1) * a.groups;  // KV heads of the whole model
 
-    // One thread per (tile, token, row) at a time: heads -> KV-head sums -> total -> residual.
+    // ---- per-lane constants of the fragment loads ---------------------------------------
+    const int r8 = lane & 7;
+    // Weights (A operand): matrices ordered (rows 0-7, rows 8-15) x (k, k + 8).
+    const uint32_t w_row_off = (((lane >> 3) & 1) * 8 + r8) * 128;
+    const uint32_t w_xor = ((lane >> 4) ^ r8) << 4;
+    // Activations (B operand): matrices ordered k, k + 8, k + 16, k + 24 of token r8.
+    const uint32_t x_lane = smem_u32(s_x) + r8 * x_pitch + (lane >> 3) * 16;
+    const int gid = lane >> 2;
+    const int tig = lane & 3;
+
+    int cons_stage = 0;
+    uint32_t cons_parity = 0;
     bool timed_out = false;
-    for (int o = threadIdx.x; o < a.tiles_per_cta * kTileOutputs; o += kProjThreads) {
-        const int t = o >> 7;
-        const int b = (o & 127) >> 4;
-        const int n = (blockIdx.x * a.tiles_per_cta + t) * kTileRows + (o & 15);
-        if (b >= a.batch || n >= a.hidden || timed_out) continue;
-        const float* part =
-            s_part + (int64_t)t * a.heads * kTileOutputs + (o & 15) * kProjTokens + b;
-        const int per_group = a.heads / a.groups;
-        float sums[kMaxLocalGroups];
+#pragma unroll 1
+    for (int tile = worker; tile < tiles && !timed_out; tile += workers) {
+        // One accumulator per block of 16 columns of a head (eight independent MMA chains, so
+        // that the tensor pipe's latency is not paid per instruction); each runs over the KV
+        // head's query heads in ascending order.
+        float part[8][4];
 #pragma unroll
-        for (int lg = 0; lg < kMaxLocalGroups; ++lg) {
-            sums[lg] = 0.f;
-            if (lg < a.groups) {
-                const float* p = part + (int64_t)lg * per_group * kTileOutputs;
-                float s = p[0];
-                for (int j = 1; j < per_group; ++j) s += p[j * kTileOutputs];
-                sums[lg] = s;
-            }
+        for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) part[ks][i] = 0.f;
         }
-        float total = 0.f;
-        if (!SHARDED) {
-#pragma unroll
-            for (int lg = 0; lg < kMaxLocalGroups; ++lg) {
-                if (lg < a.groups) total += sums[lg];
+#pragma unroll 1
+        for (int head = 0; head < per_group; ++head) {
+            const uint32_t tile_addr = ring + cons_stage * kHeadTileBytes + w_row_off;
+            if (!wait_full(bars + cons_stage * 8, cons_parity)) {
+                timed_out = true;
+                break;
             }
-        } else {
-            const uint32_t step = s_step;
-            const uint64_t per_token = (uint64_t)a.hidden;
+            const uint32_t x_addr = x_lane + head * (kHeadDim * 2);
 #pragma unroll
-            for (int lg = 0; lg < kMaxLocalGroups; ++lg) {
-                if (lg < a.groups) {
-                    const uint64_t word = ((uint64_t)lg * a.batch + b) * per_token + n;
-                    for (int p = 0; p < g.nranks; ++p) {
-                        if (p == g.rank) continue;
-                        push_word(window_slot(g.windows[p], step, g.nranks, g.rank, g.slot_bytes) +
-                                      word,
-                                  step, __float_as_uint(sums[lg]));
-                    }
+            for (int kp = 0; kp < 4; ++kp) {  // 32 columns per pass, ascending
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(x_addr + kp * 64, b0, b1, b2, b3);
+                const uint32_t box = tile_addr + (kp >> 1) * kBoxBytes;
+                uint32_t a0, a1, a2, a3;
+                ldmatrix_x4(box + ((((kp & 1) * 4) << 4) ^ w_xor), a0, a1, a2, a3);
+                mma_bf16_16816(part[2 * kp], a0, a1, a2, a3, b0, b1);
+                ldmatrix_x4(box + ((((kp & 1) * 4 + 2) << 4) ^ w_xor), a0, a1, a2, a3);
+                mma_bf16_16816(part[2 * kp + 1], a0, a1, a2, a3, b2, b3);
+            }
+            if (++cons_stage == a.stages) {
+                cons_stage = 0;
+                cons_parity ^= 1u;
+            }
+            __syncwarp();
+            issue();  // the stage is free again
+        }
+        if (timed_out) break;
+        // The eight block sums, added in ascending order.
+        float acc[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc[i] = part[0][i];
+#pragma unroll
+            for (int ks = 1; ks < 8; ++ks) acc[i] += part[ks][i];
+        }
+        // acc[0..1]: row gid, tokens 2 tig and 2 tig + 1; acc[2..3]: row gid + 8. With a single
+        // KV head in the whole model that is the result; otherwise each sum becomes a tagged
+        // word, here or (sharded) in every rank's window, for the second phase below.
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int b = 2 * tig + (i & 1);
+            if (b >= a.batch) continue;
+            const int n = tile * kTileRows + gid + (i >> 1) * 8;
+            const int64_t token_word = (int64_t)b * a.hidden + n;
+            if (count == 1) {
+                __nv_bfloat16* out = a.residual + token_word;
+                *out = __float2bfloat16(__bfloat162float(*out) + (0.f + acc[i]));
+                continue;
+            }
+            const int64_t word = (int64_t)lg * a.batch * a.hidden + token_word;
+            if (!SHARDED) {
+                push_word(a.words + word, local_step, __float_as_uint(acc[i]));
+            } else {
+                for (int p = 0; p < g.nranks; ++p) {
+                    push_word(window_slot(g.windows[p], step, g.nranks, g.rank, g.slot_bytes) + word,
+                              step, __float_as_uint(acc[i]));
                 }
             }
-            const unsigned long long start = global_timer();
-            uint8_t* mine = g.windows[g.rank];
-            for (int r = 0; r < g.nranks && !timed_out; ++r) {
-#pragma unroll
-                for (int lg = 0; lg < kMaxLocalGroups; ++lg) {
-                    if (lg < a.groups && !timed_out) {
-                        float v = sums[lg];
-                        if (r != g.rank) {
-                            const uint64_t word = ((uint64_t)lg * a.batch + b) * per_token + n;
-                            uint32_t bits = 0;
-                            if (poll_word(window_slot(mine, step, g.nranks, r, g.slot_bytes) + word,
-                                          step, start, &bits)) {
-                                v = __uint_as_float(bits);
-                            } else {
-                                timed_out = true;
-                            }
-                        }
-                        total += v;
-                    }
-                }
-            }
-        }
-        if (!timed_out) {
-            __nv_bfloat16* out = a.residual + (int64_t)b * a.hidden + n;
-            *out = __float2bfloat16(__bfloat162float(*out) + total);
         }
     }
-    if (SHARDED) {
-        if (timed_out) s_timed_out = 1;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            WindowCtrl* ctrl = window_ctrl(g.windows[g.rank], g.slot_bytes, g.nranks);
-            if (s_timed_out) {
-                ctrl->status = 1;
-                if (g.status != nullptr) atomicExch(g.status, 2);
+
+    // ---- second phase: every CTA finishes its share of the outputs -----------------------
+    // All KV-head sums of the model, own ones included, are read back as words (those of other
+    // CTAs and ranks may still be on their way: bounded polls), added in ascending order, and
+    // the residual is updated. Nothing in the streaming loop above ever waits for another warp.
+    if (count > 1) {
+        const int64_t outputs = (int64_t)a.batch * a.hidden;
+        for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < outputs && !timed_out;
+             o += (int64_t)gridDim.x * blockDim.x) {
+            auto word_at = [&](int idx, uint32_t* tag) -> const unsigned long long* {
+                const int r = idx / a.groups;
+                const int64_t word = (int64_t)(idx - r * a.groups) * outputs + o;
+                if (SHARDED) {
+                    *tag = step;
+                    return window_slot(g.windows[g.rank], step, g.nranks, r, g.slot_bytes) + word;
+                }
+                *tag = local_step;
+                return a.words + word;
+            };
+            __nv_bfloat16* out = a.residual + o;
+            const float before = __bfloat162float(*out);  // travels while the words are polled
+            float total = 0.f;
+            const unsigned long long start = global_timer();
+            for (int base = 0; base < count; base += 8) {
+                // All loads of a batch of eight travel together; late words are asked for again.
+                unsigned long long got[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    uint32_t tag;
+                    if (base + i < count) got[i] = load_word(word_at(base + i, &tag));
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (base + i >= count) continue;
+                    uint32_t tag;
+                    const unsigned long long* src = word_at(base + i, &tag);
+                    while ((uint32_t)(got[i] >> 32) != tag) {
+                        if (global_timer() - start > kGatherWaitNs) {
+                            timed_out = true;
+                            break;
+                        }
+                        got[i] = load_word(src);
+                    }
+                    total += __uint_as_float((uint32_t)got[i]);
+                }
             }
-            // The last CTA to finish advances the step counter for the next launch.
-            __threadfence();
+            if (!timed_out) *out = __float2bfloat16(before + total);
+        }
+    }
+    if (timed_out) s_timed_out = 1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (s_timed_out && a.status != nullptr) atomicExch(a.status, 2);
+        // The last CTA to finish advances the launch counters for the next launch.
+        if (a.ctrl != nullptr) {
+            const uint32_t ticket = atomicAdd(&a.ctrl->ticket_out, 1u);
+            if (ticket == gridDim.x - 1) {
+                a.ctrl->ticket_out = 0;
+                a.ctrl->step = s_local_step;
+            }
+        }
+        if (SHARDED) {
+            WindowCtrl* ctrl = window_ctrl(g.windows[g.rank], g.slot_bytes, g.nranks);
+            if (s_timed_out) ctrl->status = 1;
             const uint32_t ticket = atomicAdd(&ctrl->ticket_out, 1u);
             if (ticket == gridDim.x - 1) {
                 ctrl->ticket_out = 0;
@@ -213,7 +329,14 @@ __global__ void __launch_bounds__(kProjThreads, 3)
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int validate(const gqa_oproj_params* p, int* tiles_per_cta, int* heads_per_warp) {
+constexpr size_t kCtrlBytes = 256;
+
+size_t workspace_bytes(int hidden, int groups) {
+    if (groups <= 1) return 0;
+    return kCtrlBytes + (size_t)groups * kProjTokens * hidden * sizeof(unsigned long long);
+}
+
+int validate(const gqa_oproj_params* p) {
     if (p == nullptr) return GQA_ERR_NULL;
     if (p->attn_out == nullptr || p->weight == nullptr || p->residual == nullptr) {
         return GQA_ERR_NULL;
@@ -222,35 +345,83 @@ int validate(const gqa_oproj_params* p, int* tiles_per_cta, int* heads_per_warp)
         return GQA_ERR_SHAPE;
     }
     const int heads = p->num_q_heads;
-    if (heads <= 0 || p->num_kv_heads <= 0 || p->num_kv_heads > kMaxLocalGroups ||
-        heads % p->num_kv_heads != 0) {
-        return GQA_ERR_SHAPE;
-    }
-    if (heads % kProjWarps == 0) {
-        *tiles_per_cta = 1;
-        *heads_per_warp = heads / kProjWarps;
-    } else if (heads == 1 || heads == 2 || heads == 4) {
-        *tiles_per_cta = kProjWarps / heads;
-        *heads_per_warp = 1;
-    } else {
-        return GQA_ERR_SHAPE;
-    }
-    if ((size_t)*tiles_per_cta * heads * kTileOutputs * sizeof(float) > 48 * 1024) {
+    if (heads <= 0 || p->num_kv_heads <= 0 || heads % p->num_kv_heads != 0 ||
+        heads / p->num_kv_heads > kMaxHeadsPerGroup) {
         return GQA_ERR_SHAPE;
     }
     if (p->weight_ld < (int64_t)heads * kHeadDim || p->weight_ld % 8 != 0) return GQA_ERR_SHAPE;
     if (!aligned16(p->attn_out) || !aligned16(p->weight)) return GQA_ERR_ALIGN;
+    const size_t need = workspace_bytes(p->hidden, p->num_kv_heads);
+    if (need != 0) {
+        if (p->workspace == nullptr) return GQA_ERR_NULL;
+        if (p->workspace_bytes < need) return GQA_ERR_WORKSPACE;
+        if (!aligned16(p->workspace)) return GQA_ERR_ALIGN;
+    }
     return GQA_OK;
 }
 
+size_t smem_bytes(int warps, int stages, int per_group) {
+    return 1024 + (size_t)warps * stages * kHeadTileBytes +
+           (size_t)kProjTokens * (per_group * kHeadDim * 2 + 16) + (size_t)warps * stages * 8;
+}
+
+// Ring depth per warp and CTAs per SM; "GQA_OPROJ_SHAPE=stages,ctas" overrides (tuning).
+void oproj_shape(int* stages, int* ctas_per_sm) {
+    *stages = 3;
+    *ctas_per_sm = 3;
+    static const char* env = std::getenv("GQA_OPROJ_SHAPE");
+    int s = 0, c = 0;
+    if (env != nullptr && std::sscanf(env, "%d,%d", &s, &c) == 2 && s >= 1 && s <= 12 && c >= 1 &&
+        c <= 4) {
+        *stages = s;
+        *ctas_per_sm = c;
+    }
+}
+
 int run(const gqa_oproj_params* p, gqa_comm* comm) {
-    int tiles_per_cta = 0, heads_per_warp = 0;
-    const int rc = validate(p, &tiles_per_cta, &heads_per_warp);
+    const int rc = validate(p);
     if (rc != GQA_OK) return rc;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(p->stream);
+    int32_t sms = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        return GQA_ERR_CUDA;
+    }
+    const int groups = p->num_kv_heads;
+    const int per_group = p->num_q_heads / groups;
     const int tiles = p->hidden / kTileRows;
-    const int grid = (tiles + tiles_per_cta - 1) / tiles_per_cta;
-    const size_t smem = (size_t)tiles_per_cta * p->num_q_heads * kTileOutputs * sizeof(float);
+    int stages = 0, ctas_per_sm = 0;
+    oproj_shape(&stages, &ctas_per_sm);
+    // Every warp gets the same number of tiles (k) of its KV head, or one fewer: as many
+    // warps as the GPU holds at once, but no more than tiles; small problems use narrower
+    // CTAs so that they still reach every SM.
+    int ctas_per_group = ctas_per_sm * sms / groups;
+    if (ctas_per_group < 1) ctas_per_group = 1;
+    const int k = (tiles + ctas_per_group * kProjMaxWarps - 1) / (ctas_per_group * kProjMaxWarps);
+    const int workers = (tiles + k - 1) / k;  // per KV head
+    int warps = kProjMaxWarps;
+    if ((int64_t)workers * groups < (int64_t)sms * kProjMaxWarps) {
+        warps = (int)((int64_t)workers * groups / sms);
+        if (warps < 1) warps = 1;
+    }
+    const int grid = (workers + warps - 1) / warps * groups;
+    const size_t smem = smem_bytes(warps, stages, per_group);
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(oproj_residual_kernel<false>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+        if (attr_err == cudaSuccess) {
+            attr_err = cudaFuncSetAttribute(oproj_residual_kernel<true>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+        }
+    });
+    if (attr_err != cudaSuccess || smem > (size_t)kMaxSmem) return GQA_ERR_CUDA;
+    CUtensorMap wmap;
+    const int mrc = cached_matrix_map(p->weight, (int64_t)p->num_q_heads * kHeadDim, p->hidden,
+                                      p->weight_ld, &wmap);
+    if (mrc != GQA_OK) return mrc;
     // More than 8 tokens: one pass over the weights per 8 (each its own exchange step).
     for (int b0 = 0; b0 < p->batch; b0 += kProjTokens) {
         OprojArgs a;
@@ -258,26 +429,29 @@ int run(const gqa_oproj_params* p, gqa_comm* comm) {
         a.batch = p->batch - b0 < kProjTokens ? p->batch - b0 : kProjTokens;
         a.x = static_cast<const __nv_bfloat16*>(p->attn_out) +
               (int64_t)b0 * p->num_q_heads * kHeadDim;
-        a.w = static_cast<const __nv_bfloat16*>(p->weight);
         a.residual = static_cast<__nv_bfloat16*>(p->residual) + (int64_t)b0 * p->hidden;
-        a.ld = p->weight_ld;
+        if (groups > 1) {
+            a.ctrl = static_cast<WindowCtrl*>(p->workspace);
+            a.words = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(p->workspace) +
+                                                            kCtrlBytes);
+        }
+        a.status = p->status_dev;
         a.hidden = p->hidden;
         a.heads = p->num_q_heads;
-        a.groups = p->num_kv_heads;
-        a.tiles_per_cta = tiles_per_cta;
-        a.heads_per_warp = heads_per_warp;
+        a.groups = groups;
+        a.stages = stages;
         PeerGatherArgs g;
         std::memset(&g, 0, sizeof(g));
         cudaError_t e;
         if (comm != nullptr && gqa_comm_nranks(comm) > 1) {
-            const size_t bytes = (size_t)p->num_kv_heads * a.batch * p->hidden * sizeof(float);
+            const size_t bytes = (size_t)groups * a.batch * p->hidden * sizeof(float);
             const int crc = comm_peer_args(comm, bytes, p->status_dev, &g);
             if (crc != GQA_OK) return crc;
-            e = launch_pdl(oproj_residual_kernel<true>, dim3(grid), dim3(kProjThreads), smem,
-                           stream, a, g);
+            e = launch_pdl(oproj_residual_kernel<true>, dim3(grid), dim3(32 * warps), smem, stream,
+                           wmap, a, g);
         } else {
-            e = launch_pdl(oproj_residual_kernel<false>, dim3(grid), dim3(kProjThreads), smem,
-                           stream, a, g);
+            e = launch_pdl(oproj_residual_kernel<false>, dim3(grid), dim3(32 * warps), smem,
+                           stream, wmap, a, g);
         }
         if (e != cudaSuccess) return GQA_ERR_CUDA;
     }
@@ -288,6 +462,11 @@ int run(const gqa_oproj_params* p, gqa_comm* comm) {
 }  // namespace gqa
 
 extern "C" {
+
+size_t gqa_oproj_workspace_bytes(int32_t hidden, int32_t num_kv_heads) {
+    if (hidden <= 0 || num_kv_heads <= 0) return 0;
+    return gqa::workspace_bytes(hidden, num_kv_heads);
+}
 
 int gqa_oproj_residual(const gqa_oproj_params* p) { return gqa::run(p, nullptr); }
 

@@ -109,7 +109,7 @@ def main() -> None:
 
     # The same through the NVLink peer-store gather, step after step (the two window halves
     # alternate) and inside a replayed CUDA graph (the step counter lives on the device).
-    comm.enable_peer_gather(batch * per_q * d * 2)
+    comm.enable_peer_gather(max(batch * per_q * d * 2, 4 * per_kv * 3 * 256))
     for _ in range(5):
         again = run(q_l, k_l, v_l, per_q, per_kv, sharded=True)
         assert torch.equal(again.view(torch.int16), full.view(torch.int16)), "peer gather != unsharded"
@@ -158,6 +158,30 @@ def main() -> None:
     torch.cuda.synchronize()
     whole32 = sharding.unshard_output(gathered32)
     assert torch.equal(whole32.view(torch.int32), full32.view(torch.int32)), "fp32 sharded != unsharded"
+
+    # Output projection behind attention: every rank multiplies its own heads' columns and the
+    # per-KV-head sums travel through the peer windows. Every rank ends with the complete
+    # residual, bit-equal to the unsharded result.
+    hidden, tokens = 256, 3
+    attn = H.rand_bits(rng, (tokens, hq, d))
+    w_o = cases.to_bf16_bits(rng.standard_normal((hidden, hq * d), dtype=np.float32) / np.float32(90.0))
+    res0 = H.rand_bits(rng, (tokens, hidden))
+    want_res = H.bf16_tensor(res0, dev).clone()
+    gqa.oproj_residual(H.bf16_tensor(attn, dev), H.bf16_tensor(w_o, dev), want_res, num_kv_heads=hkv,
+                       workspace=gqa.oproj_workspace(hidden, hkv, dev))
+    w_dev = H.bf16_tensor(w_o, dev)
+    attn_l = H.bf16_tensor(np.ascontiguousarray(attn[:, rank * per_q:(rank + 1) * per_q]), dev)
+    ws_l = gqa.oproj_workspace(hidden, per_kv, dev)
+    for _ in range(3):  # consecutive steps alternate between the two halves of the windows
+        got_res = H.bf16_tensor(res0, dev).clone()
+        gqa.oproj_residual(attn_l, w_dev[:, rank * per_q * d:], got_res, num_kv_heads=per_kv,
+                           workspace=ws_l, comm=comm, status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert torch.equal(got_res.view(torch.int16), want_res.view(torch.int16)), "sharded o-proj"
+    want_np = oracle.gemv_add(attn.reshape(tokens, -1), w_o, res0, accum=1)
+    dist_ulp = H.bf16_ulp_distance(H.bits_of(got_res), want_np)
+    assert dist_ulp.max() <= 1, int(dist_ulp.max())
 
     # The host-buffer step with the gather inside.
     layout_l = gqa.layout_pool(num_blocks, block_tokens, per_kv)

@@ -33,9 +33,12 @@ def run(gqa, x_bits, w_bits, r_bits, *, kv_heads, **kw):
     x = H.bf16_tensor(x_bits).reshape(batch, k // 128, 128)
     w = H.bf16_tensor(w_bits)
     r = H.bf16_tensor(r_bits).clone()
-    gqa.oproj_residual(x, w, r, num_kv_heads=kv_heads, **kw)
+    ws = gqa.oproj_workspace(r.shape[-1], kv_heads, "cuda:0")
+    for _ in range(2):  # the second call finds the workspace as the first one left it
+        out = r.clone()
+        gqa.oproj_residual(x, w, out, num_kv_heads=kv_heads, workspace=ws, **kw)
     torch.cuda.synchronize()
-    return H.bits_of(r)
+    return H.bits_of(out)
 
 
 def check(got, want, where):
@@ -49,14 +52,15 @@ def test_matches_reference_kernel_output(gqa, golden_proj, index):
     name, n, k = cases.OPROJ_CASES[index]
     x, w, r = cases.oproj_inputs(index)
     heads = k // 128
-    for kv_heads in sorted({1, min(heads, 2), min(heads, 8)}):
+    for kv_heads in [kv for kv in (1, 2, 8) if heads % kv == 0 and heads // kv <= 16]:
         got = run(gqa, x[None], w, r[None], kv_heads=kv_heads)[0]
         check(got, golden_proj[f"oproj/{name}/out"], (name, kv_heads, "reference kernel"))
         check(got, oracle.gemv_add(x, w, r, accum=1), (name, kv_heads, "fp64 oracle"))
 
 
 @pytest.mark.parametrize("batch", [1, 3, 8, 11])
-@pytest.mark.parametrize("heads,kv_heads", [(1, 1), (2, 1), (4, 2), (8, 8), (16, 8), (40, 8)])
+@pytest.mark.parametrize("heads,kv_heads", [(1, 1), (2, 1), (4, 2), (8, 8), (16, 8), (40, 8),
+                                            (3, 1), (12, 1), (32, 2)])
 def test_batches_and_head_counts(gqa, batch, heads, kv_heads):
     rng = np.random.default_rng(1000 * batch + heads)
     n, k = 80, heads * 128
@@ -84,7 +88,8 @@ def test_column_slice_of_a_wider_matrix(gqa):
     want = run(gqa, x, packed, r, kv_heads=2)
     w_dev = H.bf16_tensor(w_full)
     res = H.bf16_tensor(r).clone()
-    gqa.oproj_residual(H.bf16_tensor(x).reshape(2, heads, 128), w_dev[:, first:], res, num_kv_heads=2)
+    gqa.oproj_residual(H.bf16_tensor(x).reshape(2, heads, 128), w_dev[:, first:], res,
+                       num_kv_heads=2, workspace=gqa.oproj_workspace(n, 2, "cuda:0"))
     torch.cuda.synchronize()
     assert np.array_equal(H.bits_of(res), want)
     check(want, oracle.gemv_add(x, packed, r, accum=1), "fp64 oracle")
@@ -110,13 +115,21 @@ def test_rejects_unsupported_shapes(gqa):
     x = torch.zeros(1, 8, 128, dtype=torch.bfloat16, device="cuda:0")
     w = torch.zeros(64, 1024, dtype=torch.bfloat16, device="cuda:0")
     r = torch.zeros(1, 64, dtype=torch.bfloat16, device="cuda:0")
+    ws = gqa.oproj_workspace(64, 8, "cuda:0")
     with pytest.raises(gqa.GqaError):
-        gqa.oproj_residual(x, w, r[:, :56], num_kv_heads=8)       # rows not a multiple of 16
+        gqa.oproj_residual(x, w, r[:, :56], num_kv_heads=8, workspace=ws)  # rows % 16 != 0
     with pytest.raises(gqa.GqaError):
-        gqa.oproj_residual(x, w, r, num_kv_heads=3)               # heads not divisible
+        gqa.oproj_residual(x, w, r, num_kv_heads=3, workspace=ws)       # heads not divisible
     with pytest.raises(gqa.GqaError):
-        gqa.oproj_residual(x[:, :3], w, r, num_kv_heads=1)        # 3 heads: no warp layout
+        gqa.oproj_residual(x, w, r, num_kv_heads=8)                     # workspace missing
     with pytest.raises(gqa.GqaError):
-        gqa.oproj_residual(x, w, r, num_kv_heads=8, weight_ld=512)  # pitch below the columns
+        gqa.oproj_residual(x, w, r, num_kv_heads=8, workspace=ws[:64])  # workspace too small
     with pytest.raises(gqa.GqaError):
-        gqa.oproj_residual(x, w.view(-1)[4:4 + 64 * 1016].view(64, 1016), r, num_kv_heads=8)
+        gqa.oproj_residual(x, w, r, num_kv_heads=8, workspace=ws, weight_ld=512)  # pitch < columns
+    with pytest.raises(gqa.GqaError):
+        gqa.oproj_residual(x, w.view(-1)[4:4 + 64 * 1016].view(64, 1016), r, num_kv_heads=8,
+                           workspace=ws)                                # weight not 16-byte aligned
+    wide = torch.zeros(1, 34, 128, dtype=torch.bfloat16, device="cuda:0")
+    with pytest.raises(gqa.GqaError):
+        gqa.oproj_residual(wide, torch.zeros(64, 34 * 128, dtype=torch.bfloat16, device="cuda:0"),
+                           r, num_kv_heads=2, workspace=ws)             # 17 heads per KV head
