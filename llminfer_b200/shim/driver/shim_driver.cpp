@@ -44,7 +44,37 @@ tensor::Tensor host_bf16(const std::vector<uint16_t>& data, std::vector<int32_t>
 
 }  // namespace
 
+// "oproj dir n k": residual += x . W^T through kernel::get_fused_gemv_add_kernel, the way
+// the reference's model calls its output projection.
+int run_projection(const std::string& dir, int32_t n, int32_t k) {
+    const auto cuda = base::DeviceType::DeviceCUDA;
+    tensor::Tensor x = host_bf16(read_file(dir + "/x.bin", k), {k});
+    tensor::Tensor w = host_bf16(read_file(dir + "/w.bin", static_cast<size_t>(n) * k), {n, k});
+    tensor::Tensor r = host_bf16(read_file(dir + "/r.bin", n), {n});
+    x.to_cuda();
+    w.to_cuda();
+    r.to_cuda();
+    auto config = std::make_shared<kernel::CudaConfig>();
+    config->create();
+    for (int rep = 0; rep < 2; ++rep) {  // the second call reuses the shim's scratch
+        if (rep == 1) {
+            tensor::Tensor again = host_bf16(read_file(dir + "/r.bin", n), {n});
+            again.to_cuda();
+            r = again;
+        }
+        kernel::get_fused_gemv_add_kernel(cuda)(x, w, r, config->stream);
+        CHECK(cudaStreamSynchronize(config->stream) == cudaSuccess);
+    }
+    r.to_cpu();
+    write_file(dir + "/r_out.bin", r.ptr<uint16_t>(), r.byte_size());
+    std::printf("shim_driver ok\n");
+    return 0;
+}
+
 int main(int argc, char** argv) {
+    if (argc == 5 && std::string(argv[1]) == "oproj") {
+        return run_projection(argv[2], std::atoi(argv[3]), std::atoi(argv[4]));
+    }
     if (argc != 8) {
         std::fprintf(stderr, "usage: %s dir head_num kv_head_num layer_num layer_id max_seq_len pos\n",
                      argv[0]);

@@ -32,6 +32,12 @@ using SinCosCacheKernel = void (*)(const tensor::Tensor& sin_cache, const tensor
                                    int32_t head_dim, int32_t max_seq_len, void* stream);
 SinCosCacheKernel get_sin_cos_cache_kernel(base::DeviceType device_type);
 
+// Output projection with residual add, the step behind attention
+// (code/source/op/kernel/kernel_interface.h:53-59): output[n] += dot(input, weight[n]).
+using FusedGEMVAddKernel = void (*)(const tensor::Tensor& input, const tensor::Tensor& weight,
+                                    const tensor::Tensor& output, void* stream);
+FusedGEMVAddKernel get_fused_gemv_add_kernel(base::DeviceType device_type);
+
 // The functions behind the getters, exported with the reference's names so that the
 // reference's own kernel_interface.cpp links against this library unchanged.
 void mha_kernel_cu(const tensor::Tensor& query, const tensor::Tensor& key_cache,
@@ -45,6 +51,8 @@ void fused_qk_norm_rope_kernel_cu(const tensor::Tensor& query, const tensor::Ten
                                   int32_t dim, int32_t kv_dim, int32_t head_dim, void* stream);
 void sin_cos_cache_precompute_cu(const tensor::Tensor& sin_cache, const tensor::Tensor& cos_cache,
                                  int32_t head_dim, int32_t max_seq_len, void* stream);
+void fused_gemv_add_kernel_cu(const tensor::Tensor& input, const tensor::Tensor& weight,
+                              const tensor::Tensor& output, void* stream);
 
 }  // namespace kernel
 

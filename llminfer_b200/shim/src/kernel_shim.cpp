@@ -1,13 +1,15 @@
 // The reference's kernel entry points for the attention path, implemented on the C ABI of
 // libgqa_b200.so. Signatures, argument meaning and failure behaviour (abort on a broken
 // precondition) follow code/source/op/kernel/cuda/mha_kernel.cu:440-529,
-// code/source/op/kernel/cuda/rmsnorm_kernel.cu:257-290 and
-// code/source/op/kernel/cuda/rope_kernel.cu:23-46. This file only uses members that the
+// code/source/op/kernel/cuda/rmsnorm_kernel.cu:257-290,
+// code/source/op/kernel/cuda/rope_kernel.cu:23-46 and, for the projection behind attention,
+// code/source/op/kernel/cuda/matmul_kernel.cu:172-208. This file only uses members that the
 // reference's tensor::Tensor also has, so it compiles against either set of headers.
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
+#include "base/alloc.h"
 #include "gqa_b200.h"
 #include "op/kernel_interface.h"
 
@@ -143,6 +145,63 @@ void sin_cos_cache_precompute_cu(const tensor::Tensor& sin_cache, const tensor::
 }
 
 namespace {
+
+// Scratch of the projection (per-KV-head sums in flight), owned by the shim the way the
+// reference's model owns its buffers; one host thread drives the kernels, as in the reference.
+void* projection_workspace(size_t bytes, void* stream) {
+    static void* ptr = nullptr;
+    static size_t capacity = 0;
+    if (bytes > capacity) {
+        auto alloc = base::CUDADeviceAllocatorFactory::get_instance();
+        if (ptr != nullptr) alloc->release(ptr);
+        ptr = alloc->allocate(bytes);
+        require(ptr != nullptr, "projection workspace allocated");
+        alloc->memset_zero(ptr, bytes, stream, true);
+        capacity = bytes;
+    }
+    return ptr;
+}
+
+}  // namespace
+
+void fused_gemv_add_kernel_cu(const tensor::Tensor& input, const tensor::Tensor& weight,
+                              const tensor::Tensor& output, void* stream) {
+    require(!input.is_empty() && input.dims_size() == 1, "input is a vector");
+    require(!weight.is_empty() && weight.dims_size() == 2, "weight is a matrix");
+    require(!output.is_empty() && output.dims_size() == 1, "output is a vector");
+    require(input.data_type() == base::DataType::DataTypeBf16 &&
+                weight.data_type() == base::DataType::DataTypeBf16 &&
+                output.data_type() == base::DataType::DataTypeBf16, "tensors are BF16");
+    require(on_cuda(input) && on_cuda(weight) && on_cuda(output),
+            "tensors live on the CUDA device");
+    const int32_t n = weight.get_dim(0);
+    const int32_t k = weight.get_dim(1);
+    require(input.get_dim(0) == k && output.get_dim(0) == n, "shapes agree with the weight");
+    require(k % 128 == 0 && n % 16 == 0, "columns are whole heads of 128, rows a multiple of 16");
+    // Any grouping of the column heads gives the same sum up to FP32 rounding; take groups of
+    // up to 8 heads.
+    const int32_t heads = k / 128;
+    int32_t per_group = 8;
+    while (heads % per_group != 0) --per_group;
+
+    gqa_oproj_params p;
+    std::memset(&p, 0, sizeof(p));
+    p.batch = 1;
+    p.hidden = n;
+    p.num_q_heads = heads;
+    p.num_kv_heads = heads / per_group;
+    p.head_dim = 128;
+    p.weight_ld = k;
+    p.attn_out = input.ptr<void>();
+    p.weight = weight.ptr<void>();
+    p.residual = const_cast<void*>(output.ptr<void>());
+    p.workspace_bytes = gqa_oproj_workspace_bytes(n, p.num_kv_heads);
+    p.workspace = p.workspace_bytes != 0 ? projection_workspace(p.workspace_bytes, stream) : nullptr;
+    p.stream = stream;
+    require_ok(gqa_oproj_residual(&p), "gqa_oproj_residual");
+}
+
+namespace {
 [[noreturn]] void no_cpu_path(const char* op) {
     std::fprintf(stderr, "llminfer_b200 shim: %s has no kernel for this device type "
                          "(only DeviceCUDA is served)\n", op);
@@ -158,6 +217,11 @@ MHAKernel get_mha_kernel(base::DeviceType device_type) {
 FusedQKNormRoPEKernel get_fused_qk_norm_rope_kernel(base::DeviceType device_type) {
     if (device_type != base::DeviceType::DeviceCUDA) no_cpu_path("fused_qk_norm_rope");
     return fused_qk_norm_rope_kernel_cu;
+}
+
+FusedGEMVAddKernel get_fused_gemv_add_kernel(base::DeviceType device_type) {
+    if (device_type != base::DeviceType::DeviceCUDA) no_cpu_path("fused_gemv_add");
+    return fused_gemv_add_kernel_cu;
 }
 
 SinCosCacheKernel get_sin_cos_cache_kernel(base::DeviceType device_type) {

@@ -53,3 +53,25 @@ def test_layers_forward(tmp_path, built_lib, head_num, kv_heads, layer_num, laye
                                      max_seq_len=max_seq_len)
     abs_err, rel_err = H.errors(cases.bf16_bits_to_f32(out), want)
     assert abs_err <= 2e-2 and rel_err <= 1e-2, (abs_err, rel_err)
+
+
+@pytest.mark.parametrize("n,k", [(1024, 2048), (2560, 4096), (48, 384)])
+def test_fused_gemv_add_kernel(tmp_path, built_lib, n, k):
+    """kernel::get_fused_gemv_add_kernel(DeviceCUDA) on the reference's tensors: the output
+    projection with residual add, against the FP64 oracle."""
+    from llminfer_b200 import build
+    build.build_shim()
+    driver = ROOT / "llminfer_b200" / "lib" / "shim_driver"
+    rng = np.random.default_rng(n + k)
+    x = cases.to_bf16_bits(rng.standard_normal(k, dtype=np.float32))
+    w = cases.to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32) / np.float32(np.sqrt(k)))
+    r = cases.to_bf16_bits(rng.standard_normal(n, dtype=np.float32))
+    for name, arr in (("x", x), ("w", w), ("r", r)):
+        arr.tofile(tmp_path / f"{name}.bin")
+    run = subprocess.run([str(driver), "oproj", str(tmp_path), str(n), str(k)],
+                         capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0, run.stdout + run.stderr
+    got = np.fromfile(tmp_path / "r_out.bin", dtype=np.uint16)
+    want = oracle.gemv_add(x, w, r, accum=1)
+    assert H.bf16_ulp_distance(got, want).max() <= 1
+    assert (got != want).mean() <= 0.02
