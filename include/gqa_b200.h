@@ -368,9 +368,12 @@ int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathere
  *     residual[b, n] = bf16(float(residual[b, n]) + sum_c attn_out[b, c] * weight[n, c])
  * Replaces kernel::fused_gemv_add_kernel_cu (code/source/op/kernel/cuda/matmul_kernel.cu:
  * 143-208; single token there, `batch` tokens here, the weights are read once for all of
- * them). FP32 accumulation on tensor cores; the summation order is fixed: columns are summed
- * per query head, heads in ascending order per KV head, KV heads in ascending order. Results
- * agree with the reference kernel to one BF16 unit in the last place.
+ * them). FP32 accumulation on tensor cores; the summation order is fixed: per KV head eight
+ * accumulators (one per block of 16 columns inside a query head) run over the KV head's query
+ * heads in ascending order and are added in ascending order; KV heads are added in ascending
+ * order; the residual comes last. Results agree with the reference kernel to one BF16 unit in
+ * the last place. The weights travel by TMA: `weight` must stay valid and unchanged in place
+ * (a tensor map per matrix is cached by address).
  *
  * In a KV-head-parallel node every rank holds the columns of its own heads
  * (gqa_oproj_residual_sharded): `weight` then points at this rank's first column inside the

@@ -1,6 +1,7 @@
-"""Times the reference's own CUDA attention kernels (oracle/_ref/libref_attn.so, built by
-oracle/build_ref.sh for sm_100) on the GPU of this machine, for the BASELINE configurations
-they can run: BF16, head_dim 128, one sequence, contiguous cache. TEST INFRASTRUCTURE: the
+"""Times the reference's own CUDA attention kernels and its output projection
+(oracle/_ref/libref_attn.so, built by oracle/build_ref.sh for sm_100) on the GPU of this
+machine, for the BASELINE configurations they can run: BF16, head_dim 128, one sequence (one
+token for the projection), contiguous cache. TEST INFRASTRUCTURE: the
 numbers go into the comparison table of BASELINE.md; nothing of the product uses this file.
 
 usage: python oracle/time_ref_kernels.py
@@ -14,6 +15,10 @@ from pathlib import Path
 import torch
 
 REF = Path(__file__).resolve().parent / "_ref" / "libref_attn.so"
+PROJ_CASES = [  # name, output rows (hidden), input columns, weight copies cycled
+    ("qwen3-32b-oproj-5120x8192", 5120, 8192, 6),
+    ("qwen3-4b-oproj-2560x4096", 2560, 4096, 24),
+]
 CASES = [  # name, query heads, kv heads, cached length, layer caches cycled
     ("qwen3-4b-bf16-b1-ctx1024", 32, 8, 1024, 36),
     ("qwen3-4b-bf16-b1-ctx4096", 32, 8, 4096, 16),
@@ -58,5 +63,32 @@ def main() -> None:
                           "algorithmic_gbs": round(bytes_ / us / 1e3, 1)}))
 
 
+def projections() -> None:
+    """kernel::fused_gemv_add_kernel_cu, one token, weights cycled over more copies than L2."""
+    ref = C.CDLL(str(REF))
+    ref.ref_fused_gemv_add.restype = C.c_int
+    ref.ref_fused_gemv_add.argtypes = [C.c_void_p] * 3 + [C.c_int32] * 2 + [C.c_void_p]
+    dev = torch.device("cuda:0")
+    for name, n, k, copies in PROJ_CASES:
+        x = torch.randn(k, device=dev).to(torch.bfloat16)
+        ws = [(torch.randn(n, k, device=dev) / 64).to(torch.bfloat16) for _ in range(copies)]
+        r = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        stream = torch.cuda.current_stream().cuda_stream
+        for w in ws:
+            assert ref.ref_fused_gemv_add(x.data_ptr(), w.data_ptr(), r.data_ptr(), n, k, stream) == 0
+        torch.cuda.synchronize()
+        steps = 10 * copies
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            ref.ref_fused_gemv_add(x.data_ptr(), ws[i % copies].data_ptr(), r.data_ptr(), n, k, stream)
+        stop.record()
+        torch.cuda.synchronize()
+        us = start.elapsed_time(stop) * 1e3 / steps
+        print(json.dumps({"workload": name, "reference_cuda_us": round(us, 2),
+                          "algorithmic_gbs": round(n * k * 2 / us / 1e3, 1)}))
+
+
 if __name__ == "__main__":
+    projections()
     main()
