@@ -414,6 +414,42 @@ size_t gqa_oproj_workspace_bytes(int32_t hidden, int32_t num_kv_heads);
 int gqa_oproj_residual(const gqa_oproj_params* p);
 int gqa_oproj_residual_sharded(const gqa_oproj_params* p, gqa_comm* comm);
 
+/* ---- the projection in front of attention ------------------------------------------------ */
+
+/*
+ * Packed QKV projection, the step that precedes QK-Norm + RoPE in a decoder layer:
+ *     row n of weight [(Hq + 2 Hkv) * 128, hidden] . x[b]  ->  bf16
+ * rows [0, Hq*128) to q_out [batch, Hq*128], the next Hkv*128 rows to k_out, the last Hkv*128
+ * rows to v_out (both [batch, Hkv*128]). Replaces kernel::fused_qkv_gemv_kernel_cu
+ * (code/source/op/kernel/cuda/matmul_kernel.cu:211-298; single token there). q_out, k_out
+ * and v_out are what gqa_qk_norm_rope_append takes as q, k_new and v_new. Same kernel, same
+ * numerics contract (one BF16 unit in the last place against the reference kernel) and same
+ * workspace rules as gqa_oproj_residual. hidden is a multiple of 128. A rank of a
+ * KV-head-parallel node passes the rows of its own heads, packed the same way; there is
+ * nothing to exchange.
+ */
+typedef struct gqa_qkv_params {
+    int32_t batch;
+    int32_t hidden;       /* input columns */
+    int32_t num_q_heads;  /* output rows: (num_q_heads + 2 * num_kv_heads) * 128 */
+    int32_t num_kv_heads;
+    int32_t head_dim;     /* 128 */
+    int32_t reserved;
+    int64_t weight_ld;    /* elements between weight rows, >= hidden, % 8 == 0 */
+    const void* x;        /* [batch, hidden] bf16 */
+    const void* weight;   /* bf16 */
+    void* q_out;
+    void* k_out;
+    void* v_out;
+    void* workspace;      /* gqa_qkv_workspace_bytes() bytes, zero-filled once; null if 0 */
+    size_t workspace_bytes;
+    int32_t* status_dev;  /* may be null */
+    void* stream;
+} gqa_qkv_params;
+
+size_t gqa_qkv_workspace_bytes(int32_t hidden, int32_t num_q_heads, int32_t num_kv_heads);
+int gqa_qkv_gemv(const gqa_qkv_params* p);
+
 #ifdef __cplusplus
 }
 #endif

@@ -20,6 +20,8 @@ from .binding import (  # noqa: F401
     oproj_residual,
     oproj_workspace,
     qk_norm_rope_append,
+    qkv_gemv,
+    qkv_workspace,
     shard_plan,
     sin_cos_cache,
     status_string,

@@ -125,6 +125,27 @@ class _OprojParams(C.Structure):
     ]
 
 
+class _QkvParams(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32),
+        ("hidden", C.c_int32),
+        ("num_q_heads", C.c_int32),
+        ("num_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("reserved", C.c_int32),
+        ("weight_ld", C.c_int64),
+        ("x", C.c_void_p),
+        ("weight", C.c_void_p),
+        ("q_out", C.c_void_p),
+        ("k_out", C.c_void_p),
+        ("v_out", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+        ("status_dev", C.c_void_p),
+        ("stream", C.c_void_p),
+    ]
+
+
 _SIGNATURES = {
     "gqa_status_string": (C.c_char_p, [C.c_int]),
     "gqa_abi_version": (C.c_int, []),
@@ -166,6 +187,8 @@ _SIGNATURES = {
     "gqa_comm_destroy": (None, [C.c_void_p]),
     "gqa_decode_sharded": (C.c_int, [C.POINTER(_DecodeParams), C.c_void_p, C.c_void_p]),
     "gqa_oproj_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
+    "gqa_qkv_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
+    "gqa_qkv_gemv": (C.c_int, [C.POINTER(_QkvParams)]),
     "gqa_oproj_residual": (C.c_int, [C.POINTER(_OprojParams)]),
     "gqa_oproj_residual_sharded": (C.c_int, [C.POINTER(_OprojParams), C.c_void_p]),
 }
@@ -588,3 +611,30 @@ def oproj_residual(attn_out: torch.Tensor, weight: torch.Tensor, residual: torch
     else:
         _check(lib().gqa_oproj_residual_sharded(C.byref(p), comm._h),
                "gqa_oproj_residual_sharded")
+
+
+def qkv_workspace(hidden: int, num_q_heads: int, num_kv_heads: int, device) -> Optional[torch.Tensor]:
+    """Zero-filled workspace for qkv_gemv (None when none is needed)."""
+    nbytes = lib().gqa_qkv_workspace_bytes(hidden, num_q_heads, num_kv_heads)
+    if nbytes == 0:
+        return None
+    return torch.zeros(nbytes, dtype=torch.uint8, device=device)
+
+
+def qkv_gemv(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor, k_out: torch.Tensor,
+             v_out: torch.Tensor, *, workspace: Optional[torch.Tensor] = None,
+             status: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """Packed QKV projection: x [batch, hidden], weight [(Hq + 2 Hkv) * 128, hidden] ->
+    q_out [batch, Hq, 128], k_out and v_out [batch, Hkv, 128]."""
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    p = _QkvParams()
+    p.batch, p.hidden = x.shape
+    p.num_q_heads, p.num_kv_heads, p.head_dim = q_out.shape[1], k_out.shape[1], q_out.shape[2]
+    p.weight_ld = weight.stride(0)
+    p.x, p.weight = _ptr(x), _ptr(weight)
+    p.q_out, p.k_out, p.v_out = _ptr(q_out), _ptr(k_out), _ptr(v_out)
+    if workspace is not None:
+        p.workspace, p.workspace_bytes = _ptr(workspace), workspace.numel() * workspace.element_size()
+    p.status_dev, p.stream = _ptr(status), stream
+    _check(lib().gqa_qkv_gemv(C.byref(p)), "gqa_qkv_gemv")

@@ -54,7 +54,12 @@ constexpr int kMaxSmem = 224 * 1024;  // leaves room for the static part
 
 struct OprojArgs {
     const __nv_bfloat16* x;    // [batch][heads * 128]
-    __nv_bfloat16* residual;   // [batch][hidden]
+    __nv_bfloat16* residual;   // [batch][hidden], read and written (null in split mode)
+    __nv_bfloat16* q_out;      // split mode: rows [0, q_rows) -> q_out [batch][q_rows],
+    __nv_bfloat16* k_out;      // the next kv_rows rows -> k_out [batch][kv_rows],
+    __nv_bfloat16* v_out;      // the last kv_rows rows -> v_out [batch][kv_rows]
+    int32_t q_rows;
+    int32_t kv_rows;
     WindowCtrl* ctrl;          // launch counter of the workspace (null for one KV head)
     unsigned long long* words; // [groups][batch][hidden] tagged KV-head sums
     int32_t* status;
@@ -78,6 +83,15 @@ __device__ __forceinline__ bool wait_full(uint32_t bar, uint32_t parity) {
             if (now - start > kProjWaitNs) return false;
         }
     }
+}
+
+// Where output row n of token b goes, and whether the old value is added (the residual form).
+__device__ __forceinline__ __nv_bfloat16* output_at(const OprojArgs& a, int b, int n) {
+    if (a.residual != nullptr) return a.residual + (int64_t)b * a.hidden + n;
+    if (n < a.q_rows) return a.q_out + (int64_t)b * a.q_rows + n;
+    n -= a.q_rows;
+    if (n < a.kv_rows) return a.k_out + (int64_t)b * a.kv_rows + n;
+    return a.v_out + (int64_t)b * a.kv_rows + (n - a.kv_rows);
 }
 
 template <bool SHARDED>
@@ -239,8 +253,9 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
             const int n = tile * kTileRows + gid + (i >> 1) * 8;
             const int64_t token_word = (int64_t)b * a.hidden + n;
             if (count == 1) {
-                __nv_bfloat16* out = a.residual + token_word;
-                *out = __float2bfloat16(__bfloat162float(*out) + (0.f + acc[i]));
+                __nv_bfloat16* out = output_at(a, b, n);
+                const float before = a.residual != nullptr ? __bfloat162float(*out) : 0.f;
+                *out = __float2bfloat16(before + (0.f + acc[i]));
                 continue;
             }
             const int64_t word = (int64_t)lg * a.batch * a.hidden + token_word;
@@ -273,8 +288,9 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
                 *tag = local_step;
                 return a.words + word;
             };
-            __nv_bfloat16* out = a.residual + o;
-            const float before = __bfloat162float(*out);  // travels while the words are polled
+            __nv_bfloat16* out = output_at(a, (int)(o / a.hidden), (int)(o % a.hidden));
+            // The old value travels while the words are polled.
+            const float before = a.residual != nullptr ? __bfloat162float(*out) : 0.f;
             float total = 0.f;
             const unsigned long long start = global_timer();
             for (int base = 0; base < count; base += 8) {
@@ -336,9 +352,20 @@ size_t workspace_bytes(int hidden, int groups) {
     return kCtrlBytes + (size_t)groups * kProjTokens * hidden * sizeof(unsigned long long);
 }
 
-int validate(const gqa_oproj_params* p) {
+// Destinations of the split form (packed QKV projection); null for the residual form.
+struct SplitOut {
+    void* q;
+    void* k;
+    void* v;
+    int32_t q_rows;
+    int32_t kv_rows;
+};
+
+int validate(const gqa_oproj_params* p, const SplitOut* split) {
     if (p == nullptr) return GQA_ERR_NULL;
-    if (p->attn_out == nullptr || p->weight == nullptr || p->residual == nullptr) {
+    if (p->attn_out == nullptr || p->weight == nullptr) return GQA_ERR_NULL;
+    if (split == nullptr ? p->residual == nullptr
+                         : (split->q == nullptr || split->k == nullptr || split->v == nullptr)) {
         return GQA_ERR_NULL;
     }
     if (p->head_dim != kHeadDim || p->batch <= 0 || p->hidden <= 0 || p->hidden % kTileRows != 0) {
@@ -378,8 +405,8 @@ void oproj_shape(int* stages, int* ctas_per_sm) {
     }
 }
 
-int run(const gqa_oproj_params* p, gqa_comm* comm) {
-    const int rc = validate(p);
+int run(const gqa_oproj_params* p, const SplitOut* split, gqa_comm* comm) {
+    const int rc = validate(p, split);
     if (rc != GQA_OK) return rc;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(p->stream);
     int32_t sms = 0;
@@ -429,7 +456,15 @@ int run(const gqa_oproj_params* p, gqa_comm* comm) {
         a.batch = p->batch - b0 < kProjTokens ? p->batch - b0 : kProjTokens;
         a.x = static_cast<const __nv_bfloat16*>(p->attn_out) +
               (int64_t)b0 * p->num_q_heads * kHeadDim;
-        a.residual = static_cast<__nv_bfloat16*>(p->residual) + (int64_t)b0 * p->hidden;
+        if (split == nullptr) {
+            a.residual = static_cast<__nv_bfloat16*>(p->residual) + (int64_t)b0 * p->hidden;
+        } else {
+            a.q_rows = split->q_rows;
+            a.kv_rows = split->kv_rows;
+            a.q_out = static_cast<__nv_bfloat16*>(split->q) + (int64_t)b0 * split->q_rows;
+            a.k_out = static_cast<__nv_bfloat16*>(split->k) + (int64_t)b0 * split->kv_rows;
+            a.v_out = static_cast<__nv_bfloat16*>(split->v) + (int64_t)b0 * split->kv_rows;
+        }
         if (groups > 1) {
             a.ctrl = static_cast<WindowCtrl*>(p->workspace);
             a.words = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(p->workspace) +
@@ -468,11 +503,53 @@ size_t gqa_oproj_workspace_bytes(int32_t hidden, int32_t num_kv_heads) {
     return gqa::workspace_bytes(hidden, num_kv_heads);
 }
 
-int gqa_oproj_residual(const gqa_oproj_params* p) { return gqa::run(p, nullptr); }
+int gqa_oproj_residual(const gqa_oproj_params* p) { return gqa::run(p, nullptr, nullptr); }
 
 int gqa_oproj_residual_sharded(const gqa_oproj_params* p, gqa_comm* comm) {
     if (comm == nullptr) return GQA_ERR_NULL;
-    return gqa::run(p, comm);
+    return gqa::run(p, nullptr, comm);
+}
+
+// The packed QKV projection runs on the same kernel: its input columns are cut into "heads"
+// of 128 and groups of up to 8 heads, which only fixes the summation order.
+static int qkv_groups(int32_t hidden) {
+    const int heads = hidden / gqa::kHeadDim;
+    int per_group = 8;
+    while (heads % per_group != 0) --per_group;
+    return heads / per_group;
+}
+
+size_t gqa_qkv_workspace_bytes(int32_t hidden, int32_t num_q_heads, int32_t num_kv_heads) {
+    if (hidden <= 0 || hidden % gqa::kHeadDim != 0 || num_q_heads <= 0 || num_kv_heads <= 0) {
+        return 0;
+    }
+    return gqa::workspace_bytes((num_q_heads + 2 * num_kv_heads) * gqa::kHeadDim,
+                                qkv_groups(hidden));
+}
+
+int gqa_qkv_gemv(const gqa_qkv_params* p) {
+    if (p == nullptr) return GQA_ERR_NULL;
+    if (p->hidden <= 0 || p->hidden % gqa::kHeadDim != 0 || p->head_dim != gqa::kHeadDim ||
+        p->num_q_heads <= 0 || p->num_kv_heads <= 0) {
+        return GQA_ERR_SHAPE;
+    }
+    gqa_oproj_params o;
+    std::memset(&o, 0, sizeof(o));
+    o.batch = p->batch;
+    o.hidden = (p->num_q_heads + 2 * p->num_kv_heads) * gqa::kHeadDim;  // output rows
+    o.num_q_heads = p->hidden / gqa::kHeadDim;                          // input column heads
+    o.num_kv_heads = qkv_groups(p->hidden);
+    o.head_dim = gqa::kHeadDim;
+    o.weight_ld = p->weight_ld;
+    o.attn_out = p->x;
+    o.weight = p->weight;
+    o.workspace = p->workspace;
+    o.workspace_bytes = p->workspace_bytes;
+    o.status_dev = p->status_dev;
+    o.stream = p->stream;
+    const gqa::SplitOut split = {p->q_out, p->k_out, p->v_out, p->num_q_heads * gqa::kHeadDim,
+                                 p->num_kv_heads * gqa::kHeadDim};
+    return gqa::run(&o, &split, nullptr);
 }
 
 }  // extern "C"

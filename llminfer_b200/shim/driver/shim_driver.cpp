@@ -71,7 +71,40 @@ int run_projection(const std::string& dir, int32_t n, int32_t k) {
     return 0;
 }
 
+// "qkv dir hidden dim kv_dim": the packed QKV projection through
+// kernel::get_fused_qkv_gemv_kernel.
+int run_qkv(const std::string& dir, int32_t hidden, int32_t dim, int32_t kv_dim) {
+    const auto cuda = base::DeviceType::DeviceCUDA;
+    const int32_t rows = dim + 2 * kv_dim;
+    tensor::Tensor x = host_bf16(read_file(dir + "/x.bin", hidden), {hidden});
+    tensor::Tensor w =
+        host_bf16(read_file(dir + "/w.bin", static_cast<size_t>(rows) * hidden), {rows, hidden});
+    x.to_cuda();
+    w.to_cuda();
+    auto alloc = base::CUDADeviceAllocatorFactory::get_instance();
+    tensor::Tensor q(base::DataType::DataTypeBf16, dim, true, alloc);
+    tensor::Tensor k(base::DataType::DataTypeBf16, kv_dim, true, alloc);
+    tensor::Tensor v(base::DataType::DataTypeBf16, kv_dim, true, alloc);
+    auto config = std::make_shared<kernel::CudaConfig>();
+    config->create();
+    for (int rep = 0; rep < 2; ++rep) {
+        kernel::get_fused_qkv_gemv_kernel(cuda)(x, w, q, k, v, config->stream);
+        CHECK(cudaStreamSynchronize(config->stream) == cudaSuccess);
+    }
+    q.to_cpu();
+    k.to_cpu();
+    v.to_cpu();
+    write_file(dir + "/q_out.bin", q.ptr<uint16_t>(), q.byte_size());
+    write_file(dir + "/k_out.bin", k.ptr<uint16_t>(), k.byte_size());
+    write_file(dir + "/v_out.bin", v.ptr<uint16_t>(), v.byte_size());
+    std::printf("shim_driver ok\n");
+    return 0;
+}
+
 int main(int argc, char** argv) {
+    if (argc == 6 && std::string(argv[1]) == "qkv") {
+        return run_qkv(argv[2], std::atoi(argv[3]), std::atoi(argv[4]), std::atoi(argv[5]));
+    }
     if (argc == 5 && std::string(argv[1]) == "oproj") {
         return run_projection(argv[2], std::atoi(argv[3]), std::atoi(argv[4]));
     }

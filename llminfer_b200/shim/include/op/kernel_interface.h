@@ -38,6 +38,13 @@ using FusedGEMVAddKernel = void (*)(const tensor::Tensor& input, const tensor::T
                                     const tensor::Tensor& output, void* stream);
 FusedGEMVAddKernel get_fused_gemv_add_kernel(base::DeviceType device_type);
 
+// Packed QKV projection, the step in front of QK-Norm + RoPE
+// (code/source/op/kernel/kernel_interface.h:72-80).
+using FusedQKVGEMVKernel = void (*)(const tensor::Tensor& input, const tensor::Tensor& weight,
+                                    const tensor::Tensor& query, const tensor::Tensor& key,
+                                    const tensor::Tensor& value, void* stream);
+FusedQKVGEMVKernel get_fused_qkv_gemv_kernel(base::DeviceType device_type);
+
 // The functions behind the getters, exported with the reference's names so that the
 // reference's own kernel_interface.cpp links against this library unchanged.
 void mha_kernel_cu(const tensor::Tensor& query, const tensor::Tensor& key_cache,
@@ -53,6 +60,9 @@ void sin_cos_cache_precompute_cu(const tensor::Tensor& sin_cache, const tensor::
                                  int32_t head_dim, int32_t max_seq_len, void* stream);
 void fused_gemv_add_kernel_cu(const tensor::Tensor& input, const tensor::Tensor& weight,
                               const tensor::Tensor& output, void* stream);
+void fused_qkv_gemv_kernel_cu(const tensor::Tensor& input, const tensor::Tensor& weight,
+                              const tensor::Tensor& query, const tensor::Tensor& key,
+                              const tensor::Tensor& value, void* stream);
 
 }  // namespace kernel
 

@@ -3,7 +3,7 @@
 // precondition) follow code/source/op/kernel/cuda/mha_kernel.cu:440-529,
 // code/source/op/kernel/cuda/rmsnorm_kernel.cu:257-290,
 // code/source/op/kernel/cuda/rope_kernel.cu:23-46 and, for the projection behind attention,
-// code/source/op/kernel/cuda/matmul_kernel.cu:172-208. This file only uses members that the
+// code/source/op/kernel/cuda/matmul_kernel.cu:172-208, and in front of it, :247-298. This file only uses members that the
 // reference's tensor::Tensor also has, so it compiles against either set of headers.
 #include <cstdio>
 #include <cstdlib>
@@ -148,9 +148,11 @@ namespace {
 
 // Scratch of the projection (per-KV-head sums in flight), owned by the shim the way the
 // reference's model owns its buffers; one host thread drives the kernels, as in the reference.
-void* projection_workspace(size_t bytes, void* stream) {
-    static void* ptr = nullptr;
-    static size_t capacity = 0;
+void* projection_workspace(int which, size_t bytes, void* stream) {
+    static void* ptrs[2] = {nullptr, nullptr};
+    static size_t capacities[2] = {0, 0};
+    void*& ptr = ptrs[which];
+    size_t& capacity = capacities[which];
     if (bytes > capacity) {
         auto alloc = base::CUDADeviceAllocatorFactory::get_instance();
         if (ptr != nullptr) alloc->release(ptr);
@@ -196,9 +198,52 @@ void fused_gemv_add_kernel_cu(const tensor::Tensor& input, const tensor::Tensor&
     p.weight = weight.ptr<void>();
     p.residual = const_cast<void*>(output.ptr<void>());
     p.workspace_bytes = gqa_oproj_workspace_bytes(n, p.num_kv_heads);
-    p.workspace = p.workspace_bytes != 0 ? projection_workspace(p.workspace_bytes, stream) : nullptr;
+    p.workspace =
+        p.workspace_bytes != 0 ? projection_workspace(0, p.workspace_bytes, stream) : nullptr;
     p.stream = stream;
     require_ok(gqa_oproj_residual(&p), "gqa_oproj_residual");
+}
+
+void fused_qkv_gemv_kernel_cu(const tensor::Tensor& input, const tensor::Tensor& weight,
+                              const tensor::Tensor& query, const tensor::Tensor& key,
+                              const tensor::Tensor& value, void* stream) {
+    require(!input.is_empty() && input.dims_size() == 1, "input is a vector");
+    require(!weight.is_empty() && weight.dims_size() == 2, "weight is a matrix");
+    require(!query.is_empty() && query.dims_size() == 1 && !key.is_empty() &&
+                key.dims_size() == 1 && !value.is_empty() && value.dims_size() == 1,
+            "query, key, value are vectors");
+    require(input.data_type() == base::DataType::DataTypeBf16 &&
+                weight.data_type() == base::DataType::DataTypeBf16 &&
+                query.data_type() == base::DataType::DataTypeBf16 &&
+                key.data_type() == base::DataType::DataTypeBf16 &&
+                value.data_type() == base::DataType::DataTypeBf16, "tensors are BF16");
+    require(on_cuda(input) && on_cuda(weight) && on_cuda(query) && on_cuda(key) && on_cuda(value),
+            "tensors live on the CUDA device");
+    const int32_t hidden = input.get_dim(0);
+    const int32_t dim = query.get_dim(0);
+    const int32_t kv_dim = key.get_dim(0);
+    require(value.get_dim(0) == kv_dim && weight.get_dim(0) == dim + 2 * kv_dim &&
+                weight.get_dim(1) == hidden, "shapes agree with the weight");
+    require(hidden % 128 == 0 && dim % 128 == 0 && kv_dim % 128 == 0, "whole heads of 128");
+
+    gqa_qkv_params p;
+    std::memset(&p, 0, sizeof(p));
+    p.batch = 1;
+    p.hidden = hidden;
+    p.num_q_heads = dim / 128;
+    p.num_kv_heads = kv_dim / 128;
+    p.head_dim = 128;
+    p.weight_ld = hidden;
+    p.x = input.ptr<void>();
+    p.weight = weight.ptr<void>();
+    p.q_out = const_cast<void*>(query.ptr<void>());
+    p.k_out = const_cast<void*>(key.ptr<void>());
+    p.v_out = const_cast<void*>(value.ptr<void>());
+    p.workspace_bytes = gqa_qkv_workspace_bytes(hidden, p.num_q_heads, p.num_kv_heads);
+    p.workspace =
+        p.workspace_bytes != 0 ? projection_workspace(1, p.workspace_bytes, stream) : nullptr;
+    p.stream = stream;
+    require_ok(gqa_qkv_gemv(&p), "gqa_qkv_gemv");
 }
 
 namespace {
@@ -222,6 +267,11 @@ FusedQKNormRoPEKernel get_fused_qk_norm_rope_kernel(base::DeviceType device_type
 FusedGEMVAddKernel get_fused_gemv_add_kernel(base::DeviceType device_type) {
     if (device_type != base::DeviceType::DeviceCUDA) no_cpu_path("fused_gemv_add");
     return fused_gemv_add_kernel_cu;
+}
+
+FusedQKVGEMVKernel get_fused_qkv_gemv_kernel(base::DeviceType device_type) {
+    if (device_type != base::DeviceType::DeviceCUDA) no_cpu_path("fused_qkv_gemv");
+    return fused_qkv_gemv_kernel_cu;
 }
 
 SinCosCacheKernel get_sin_cos_cache_kernel(base::DeviceType device_type) {

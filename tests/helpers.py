@@ -46,3 +46,14 @@ def oracle_reference_layout(q_bits, k_bits, v_bits, *, layer_id, length, hkv, ma
     return oracle.mha_reference_layout(q_bits, k_bits.reshape(-1), v_bits.reshape(-1),
                                        layer_id=layer_id, pos=length - 1, hkv=hkv,
                                        max_seq_len=max_seq_len, accum=accum)
+
+
+def bf16_mismatches(got_bits: np.ndarray, want_bits: np.ndarray, ulp: int = 1,
+                    abs_tol: float = 2e-5) -> np.ndarray:
+    """Mask of values that are neither within `ulp` BF16 units in the last place nor within
+    `abs_tol` in value (near zero a unit in the last place is smaller than the FP32 rounding
+    of a long sum)."""
+    import cases
+    dist = bf16_ulp_distance(got_bits, want_bits)
+    diff = np.abs(cases.bf16_bits_to_f32(got_bits) - cases.bf16_bits_to_f32(want_bits))
+    return (dist > ulp) & (diff > abs_tol)

@@ -196,6 +196,8 @@ def test_shim_exports_the_reference_kernel_symbols(built_lib):
                    "kernel::sin_cos_cache_precompute_cu(tensor::Tensor const&",
                    "kernel::fused_gemv_add_kernel_cu(tensor::Tensor const&",
                    "kernel::get_fused_gemv_add_kernel(base::DeviceType)",
+                   "kernel::fused_qkv_gemv_kernel_cu(tensor::Tensor const&",
+                   "kernel::get_fused_qkv_gemv_kernel(base::DeviceType)",
                    "kernel::get_mha_kernel(base::DeviceType)",
                    "kernel::get_fused_qk_norm_rope_kernel(base::DeviceType)",
                    "op::MultiHeadAttention::forward()",

@@ -13,6 +13,8 @@ from oracle import oracle
 pytestmark = pytest.mark.gpu
 
 ULP_TOL = 1            # BF16 units in the last place, against the reference kernel's output
+ABS_TOL = 2e-5         # ... or this close in value: near zero a unit in the last place is
+                       # smaller than the FP32 rounding of a sum of thousands of unit-scale terms
 MISMATCH_TOL = 0.02    # share of outputs allowed to sit on the other side of a rounding boundary
 
 
@@ -42,8 +44,8 @@ def run(gqa, x_bits, w_bits, r_bits, *, kv_heads, **kw):
 
 
 def check(got, want, where):
-    dist = H.bf16_ulp_distance(got, want)
-    assert dist.max() <= ULP_TOL, (where, int(dist.max()))
+    bad = H.bf16_mismatches(got, want, ULP_TOL, ABS_TOL)
+    assert not bad.any(), (where, int(bad.sum()))
     assert (got != want).mean() <= MISMATCH_TOL, (where, float((got != want).mean()))
 
 
@@ -133,3 +135,86 @@ def test_rejects_unsupported_shapes(gqa):
     with pytest.raises(gqa.GqaError):
         gqa.oproj_residual(wide, torch.zeros(64, 34 * 128, dtype=torch.bfloat16, device="cuda:0"),
                            r, num_kv_heads=2, workspace=ws)             # 17 heads per KV head
+
+
+# ---- packed QKV projection (same kernel, split destinations) --------------------------------
+def run_qkv(gqa, x_bits, w_bits, hq, hkv):
+    batch, hidden = x_bits.shape
+    x, w = H.bf16_tensor(x_bits), H.bf16_tensor(w_bits)
+    ws = gqa.qkv_workspace(hidden, hq, hkv, "cuda:0")
+    for _ in range(2):  # the second call finds the workspace as the first one left it
+        q = torch.full((batch, hq, 128), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+        k = torch.full((batch, hkv, 128), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+        v = torch.full((batch, hkv, 128), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+        gqa.qkv_gemv(x, w, q, k, v, workspace=ws)
+    torch.cuda.synchronize()
+    return [H.bits_of(t).reshape(batch, -1) for t in (q, k, v)]
+
+
+@pytest.mark.parametrize("index", range(len(cases.QKV_CASES)))
+def test_qkv_matches_reference_kernel_output(gqa, golden_proj, index):
+    name, hidden, hq, hkv = cases.QKV_CASES[index]
+    x, w = cases.qkv_inputs(index)
+    got = run_qkv(gqa, x[None], w, hq, hkv)
+    want64 = oracle.qkv_gemv(x, w, hq * 128, hkv * 128, accum=1)
+    for part, bits, w64 in zip("qkv", got, want64):
+        check(bits[0], golden_proj[f"qkv/{name}/{part}"], (name, part, "reference kernel"))
+        check(bits[0], w64, (name, part, "fp64 oracle"))
+
+
+@pytest.mark.parametrize("batch", [1, 4, 9])
+@pytest.mark.parametrize("hidden,hq,hkv", [(128, 1, 1), (640, 2, 1), (1024, 16, 8), (5120, 8, 1)])
+def test_qkv_batches_and_shapes(gqa, batch, hidden, hq, hkv):
+    rng = np.random.default_rng(7 * batch + hidden)
+    rows = (hq + 2 * hkv) * 128
+    x = cases.to_bf16_bits(rng.standard_normal((batch, hidden), dtype=np.float32))
+    w = cases.to_bf16_bits(rng.standard_normal((rows, hidden), dtype=np.float32)
+                           / np.float32(np.sqrt(hidden)))
+    got = run_qkv(gqa, x, w, hq, hkv)
+    want = oracle.qkv_gemv(x, w, hq * 128, hkv * 128, accum=1)
+    for part, bits, w64 in zip("qkv", got, want):
+        check(bits, w64, (part, "fp64 oracle"))
+
+
+def test_qkv_feeds_the_front_stage(gqa):
+    """q, k and v of the projection are exactly what the QK-Norm + RoPE + append stage takes."""
+    rng = np.random.default_rng(99)
+    hidden, hq, hkv, max_seq_len, pos = 1024, 16, 8, 64, 17
+    x = cases.to_bf16_bits(rng.standard_normal((1, hidden), dtype=np.float32))
+    w = cases.to_bf16_bits(rng.standard_normal(((hq + 2 * hkv) * 128, hidden), dtype=np.float32) / 32)
+    norm_w = cases.to_bf16_bits(1.0 + 0.05 * rng.standard_normal(256, dtype=np.float32))
+    xq = H.bf16_tensor(x)
+    q = torch.zeros(1, hq, 128, dtype=torch.bfloat16, device="cuda:0")
+    k = torch.zeros(1, hkv, 128, dtype=torch.bfloat16, device="cuda:0")
+    v = torch.zeros(1, hkv, 128, dtype=torch.bfloat16, device="cuda:0")
+    gqa.qkv_gemv(xq, H.bf16_tensor(w), q, k, v, workspace=gqa.qkv_workspace(hidden, hq, hkv, "cuda:0"))
+    layout = gqa.layout_reference(1, max_seq_len, hkv)
+    k_cache = torch.zeros(1, max_seq_len, hkv * 128, dtype=torch.bfloat16, device="cuda:0")
+    v_cache = torch.zeros_like(k_cache)
+    q_rot = torch.zeros_like(q)
+    gqa.qk_norm_rope_append(q, k, v, H.bf16_tensor(norm_w), k_cache, v_cache, layout=layout,
+                            positions=[pos], q_out=q_rot)
+    torch.cuda.synchronize()
+    want_q, want_k, want_v = oracle.qkv_gemv(x[0], w, hq * 128, hkv * 128, accum=1)
+    # The projection's own rounding may move a value by one unit; the front stage is checked
+    # against the oracle on the projection's actual output.
+    sin, cos = oracle.sin_cos_cache(128, max_seq_len, form=1)
+    rq, rk = oracle.qk_norm_rope(H.bits_of(q)[0], H.bits_of(k)[0], norm_w, sin[pos], cos[pos], accum=1)
+    assert H.bf16_ulp_distance(H.bits_of(q_rot)[0], rq).max() <= 1
+    assert H.bf16_ulp_distance(H.bits_of(k_cache)[0, pos].reshape(hkv, 128), rk).max() <= 1
+    assert np.array_equal(H.bits_of(v_cache)[0, pos], H.bits_of(v)[0].reshape(-1))
+    check(H.bits_of(v)[0].reshape(-1), want_v, "v rows")
+    check(H.bits_of(q)[0].reshape(-1), want_q, "q rows")
+    check(H.bits_of(k)[0].reshape(-1), want_k, "k rows")
+
+
+def test_qkv_rejects_unsupported_shapes(gqa):
+    x = torch.zeros(1, 192, dtype=torch.bfloat16, device="cuda:0")
+    w = torch.zeros(3 * 128, 192, dtype=torch.bfloat16, device="cuda:0")
+    q = torch.zeros(1, 1, 128, dtype=torch.bfloat16, device="cuda:0")
+    with pytest.raises(gqa.GqaError):
+        gqa.qkv_gemv(x, w, q, q.clone(), q.clone())     # hidden is not a multiple of 128
+    x2 = torch.zeros(1, 2048, dtype=torch.bfloat16, device="cuda:0")
+    w2 = torch.zeros(3 * 128, 2048, dtype=torch.bfloat16, device="cuda:0")
+    with pytest.raises(gqa.GqaError):
+        gqa.qkv_gemv(x2, w2, q, q.clone(), q.clone())   # two column groups: workspace missing

@@ -73,5 +73,28 @@ def test_fused_gemv_add_kernel(tmp_path, built_lib, n, k):
     assert run.returncode == 0, run.stdout + run.stderr
     got = np.fromfile(tmp_path / "r_out.bin", dtype=np.uint16)
     want = oracle.gemv_add(x, w, r, accum=1)
-    assert H.bf16_ulp_distance(got, want).max() <= 1
+    assert not H.bf16_mismatches(got, want).any()
     assert (got != want).mean() <= 0.02
+
+
+@pytest.mark.parametrize("hidden,hq,hkv", [(1024, 16, 8), (2560, 32, 8)])
+def test_fused_qkv_gemv_kernel(tmp_path, built_lib, hidden, hq, hkv):
+    """kernel::get_fused_qkv_gemv_kernel(DeviceCUDA) on the reference's tensors."""
+    from llminfer_b200 import build
+    build.build_shim()
+    driver = ROOT / "llminfer_b200" / "lib" / "shim_driver"
+    rng = np.random.default_rng(hidden + hq)
+    dim, kv_dim = hq * 128, hkv * 128
+    x = cases.to_bf16_bits(rng.standard_normal(hidden, dtype=np.float32))
+    w = cases.to_bf16_bits(rng.standard_normal((dim + 2 * kv_dim, hidden), dtype=np.float32)
+                           / np.float32(np.sqrt(hidden)))
+    x.tofile(tmp_path / "x.bin")
+    w.tofile(tmp_path / "w.bin")
+    run = subprocess.run([str(driver), "qkv", str(tmp_path), str(hidden), str(dim), str(kv_dim)],
+                         capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0, run.stdout + run.stderr
+    want = oracle.qkv_gemv(x, w, dim, kv_dim, accum=1)
+    for name, w64 in zip(("q", "k", "v"), want):
+        got = np.fromfile(tmp_path / f"{name}_out.bin", dtype=np.uint16)
+        assert not H.bf16_mismatches(got, w64.reshape(-1)).any(), name
+        assert (got != w64.reshape(-1)).mean() <= 0.02, name
