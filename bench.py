@@ -195,7 +195,7 @@ def cpu_sample_us_per_layer(hq: int, hkv: int, lens, reps: int, warmup: int) -> 
     k = normal_bf16(sample_len * kv_dim)
     v = normal_bf16(sample_len * kv_dim)
     q = normal_bf16(hq * HEAD_DIM).reshape(1, hq, HEAD_DIM)
-    threads = oracle.max_threads()
+    threads = oracle.use_all_cores()
     times = []
     for i in range(warmup + reps):
         t0 = time.perf_counter()

@@ -66,6 +66,15 @@ void oracle_bf16_to_f32(const uint16_t* src, float* dst, int64_t n) {
     for (int64_t i = 0; i < n; ++i) dst[i] = bf16_bits_to_f32(src[i]);
 }
 
+/* Number of threads for the parallel loops (launchers like torchrun export OMP_NUM_THREADS=1). */
+void oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -72,6 +72,8 @@ def lib() -> C.CDLL:
         h.oracle_bf16_to_f32.restype = None
         h.oracle_bf16_to_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_int64]
         h.oracle_max_threads.restype = C.c_int
+        h.oracle_set_threads.restype = None
+        h.oracle_set_threads.argtypes = [C.c_int]
         h.oracle_gemv_add.restype = C.c_int
         h.oracle_gemv_add.argtypes = [C.c_void_p] * 4 + [C.c_int] * 3 + [C.c_int64, C.c_int]
         h.oracle_qkv_gemv.restype = C.c_int
@@ -82,6 +84,15 @@ def lib() -> C.CDLL:
 
 def max_threads() -> int:
     return lib().oracle_max_threads()
+
+
+def use_all_cores() -> int:
+    """Lets the parallel loops use every core this process may run on, whatever
+    OMP_NUM_THREADS says (torchrun exports 1). Returns the thread count."""
+    import os
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_threads(cores)
+    return max_threads()
 
 
 def f32_to_bf16(x: np.ndarray) -> np.ndarray:

@@ -92,6 +92,50 @@ def test_compute_entry_points_reject_bad_arguments_before_touching_the_device(gq
     assert handle.gqa_session_create(2, 1, 32, 8, 64, 64, C.byref(out)) == -3
 
 
+def test_projection_entry_points_validate_on_the_host(gqa):
+    """Workspace sizes are pure functions; bad shapes and missing buffers are refused before
+    any CUDA call (device pointers here are fake, non-null and aligned)."""
+    from llminfer_b200 import binding as B
+    handle = gqa.lib()
+    assert handle.gqa_oproj_residual(None) == -1
+    assert handle.gqa_qkv_gemv(None) == -1
+    assert handle.gqa_oproj_residual_sharded(None, None) == -1
+    assert handle.gqa_oproj_workspace_bytes(5120, 1) == 0           # one KV head: nothing to meet
+    assert handle.gqa_oproj_workspace_bytes(5120, 8) == 256 + 8 * 8 * 5120 * 8
+    assert handle.gqa_oproj_workspace_bytes(0, 8) == 0
+    assert handle.gqa_qkv_workspace_bytes(1024, 16, 8) == 0         # 8 column heads: one group
+    assert handle.gqa_qkv_workspace_bytes(5120, 64, 8) == 256 + 5 * 8 * (80 * 128) * 8
+    assert handle.gqa_qkv_workspace_bytes(1000, 16, 8) == 0         # not whole 128-column heads
+
+    def oproj(**kw):
+        p = B._OprojParams()
+        p.batch, p.hidden, p.num_q_heads, p.num_kv_heads, p.head_dim = 1, 64, 8, 1, 128
+        p.weight_ld = 1024
+        p.attn_out = p.weight = p.residual = 0x1000
+        for k, v in kw.items():
+            setattr(p, k, v)
+        return handle.gqa_oproj_residual(C.byref(p))
+
+    assert oproj(residual=None) == -1
+    assert oproj(hidden=56) == -3              # rows not a multiple of 16
+    assert oproj(head_dim=64) == -3
+    assert oproj(num_kv_heads=3) == -3         # heads not divisible
+    assert oproj(num_q_heads=34, num_kv_heads=2, weight_ld=34 * 128) == -3  # 17 heads per KV head
+    assert oproj(weight_ld=512) == -3          # pitch below the columns
+    assert oproj(weight_ld=1028) == -3         # pitch not a multiple of 8
+    assert oproj(weight=0x1008) == -4          # not 16-byte aligned
+    assert oproj(num_kv_heads=8) == -1         # workspace missing
+    assert oproj(num_kv_heads=8, workspace=0x2000, workspace_bytes=64) == -6
+
+    q = B._QkvParams()
+    q.batch, q.hidden, q.num_q_heads, q.num_kv_heads, q.head_dim = 1, 192, 1, 1, 128
+    q.weight_ld = 192
+    q.x = q.weight = q.q_out = q.k_out = q.v_out = 0x1000
+    assert handle.gqa_qkv_gemv(C.byref(q)) == -3   # hidden not a multiple of 128
+    q.hidden, q.weight_ld, q.v_out = 256, 256, None
+    assert handle.gqa_qkv_gemv(C.byref(q)) == -1   # a destination is missing
+
+
 def test_planner_short_context_needs_no_second_launch(gqa):
     p = plan(gqa, seq_lens=[96])
     assert p["needs_combine"] == 0 and p["workspace_bytes"] == 0
