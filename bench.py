@@ -417,6 +417,7 @@ def run_ours(args) -> None:
     # Reported beside the headline, never inside it. Weights are cycled over more copies than
     # L2 holds; sharded runs exchange the per-KV-head sums through the peer windows.
     oproj_info = None
+    qkv_info = None
     if dtype_name == "bf16" and (comm is None or args.gather == "peer"):
         hidden = HIDDEN[args.workload.split("-bf16")[0]]
         weight_bytes = hidden * hq * HEAD_DIM * 2
@@ -441,6 +442,31 @@ def run_ours(args) -> None:
                       "achieved_gbs": o_gbs, "frac_of_measured_peak": o_gbs / peak_gbs,
                       "exchange": "per-KV-head sums over the peer windows" if comm else "none"}
         del o_weights
+
+        # The step in front: packed QKV projection of this rank's heads (nothing to exchange).
+        rows = (hq + 2 * hkv) * HEAD_DIM
+        qkv_bytes = rows * hidden * 2
+        copies = max(2, -(-(256 << 20) // qkv_bytes))
+        qkv_weights = [torch.randn(rows, hidden, device=dev, dtype=torch.bfloat16) / 64
+                       for _ in range(copies)]
+        x_in = torch.randn(batch, hidden, device=dev, dtype=torch.bfloat16)
+        qkv_ws = gqa.qkv_workspace(hidden, hq, hkv, dev)
+        q_tmp = torch.empty(batch, hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        k_tmp = torch.empty(batch, hkv, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        v_tmp = torch.empty_like(k_tmp)
+
+        def qkv(_slot: int) -> None:
+            gqa.qkv_gemv(x_in, qkv_weights[calls[0] % copies], q_tmp, k_tmp, v_tmp,
+                         workspace=qkv_ws, status=status)
+            calls[0] += 1
+
+        torch.cuda.synchronize()
+        qkv_us = timed_graph(qkv, steps, warmup) * 1e3 / steps
+        assert int(status.item()) == 0, "a bounded device wait ran out"
+        qkv_gbs = qkv_bytes / (qkv_us * 1e-6) / 1e9
+        qkv_info = {"us_per_layer": qkv_us, "hidden": hidden, "weight_bytes_per_gpu": qkv_bytes,
+                    "achieved_gbs": qkv_gbs, "frac_of_measured_peak": qkv_gbs / peak_gbs}
+        del qkv_weights
 
     # ---- end to end through the host-buffer entry point -----------------------------------
     if args.attn_only:
@@ -521,7 +547,7 @@ def run_ours(args) -> None:
         "e2e": {"value": e2e_us, "unit": "us/layer", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_per_step * steps,
-        "next_rows": {"oproj_residual": oproj_info},
+        "next_rows": {"oproj_residual": oproj_info, "qkv_gemv": qkv_info},
         "clocks": clock_info,
     }
     if rank == 0 and world == 1 and args.sweep:

@@ -361,6 +361,22 @@ void gqa_comm_destroy(gqa_comm* comm);
  */
 int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathered);
 
+/*
+ * Sequence-parallel decode: every rank holds ALL heads but only a slice of each sequence's
+ * cached keys and values (for example every N-th block, or one contiguous part). p describes
+ * the LOCAL slice (local caches, local lengths, at least one key per sequence and rank). Each
+ * rank attends over its slice; the combine kernel then sends the row's record (128 channel
+ * sums relative to the slice's maximum, the maximum and the row sum) to the other ranks
+ * through the peer windows and merges all ranks' records in rank order, so p->out
+ * [batch, num_q_heads, head_dim] holds the complete attention output, bit-equal on every
+ * rank. The way past one KV head per GPU, and a way to balance ragged batches; the reference
+ * has no counterpart. Needs gqa_comm_enable_peer_gather(comm, batch * num_q_heads *
+ * (head_dim + 2) * 4) and a workspace (gqa_decode_plan's, or at least
+ * num_items * (num_q_heads / num_kv_heads) * (head_dim + 2) * 4 bytes when the plan needs
+ * none). A wait that runs out sets *status_dev to 2.
+ */
+int gqa_decode_seqpar(const gqa_decode_params* p, gqa_comm* comm);
+
 /* ---- the projection behind attention ---------------------------------------------------- */
 
 /*

@@ -12,6 +12,7 @@ from .binding import (  # noqa: F401
     ShardComm,
     decode,
     decode_plan,
+    decode_seqpar,
     decode_sharded,
     decode_static_scratch,
     layout_pool,

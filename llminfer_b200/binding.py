@@ -186,6 +186,7 @@ _SIGNATURES = {
     "gqa_comm_init": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
     "gqa_comm_destroy": (None, [C.c_void_p]),
     "gqa_decode_sharded": (C.c_int, [C.POINTER(_DecodeParams), C.c_void_p, C.c_void_p]),
+    "gqa_decode_seqpar": (C.c_int, [C.POINTER(_DecodeParams), C.c_void_p]),
     "gqa_oproj_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "gqa_qkv_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "gqa_qkv_gemv": (C.c_int, [C.POINTER(_QkvParams)]),
@@ -575,6 +576,22 @@ def decode_sharded(comm: ShardComm, gathered: torch.Tensor, q, k_cache, v_cache,
                        kw.get("plan_len_hint", 0), kw.get("status"), stream, keep,
                        kw.get("early_prefetch", False))
     _check(lib().gqa_decode_sharded(C.byref(p), comm._h, _ptr(gathered)), "gqa_decode_sharded")
+
+
+def decode_seqpar(comm: ShardComm, q, k_cache, v_cache, out, *, num_kv_heads: int,
+                  layout: KvLayout, **kw) -> None:
+    """Sequence-parallel decode: this rank's slice of every sequence, all heads; `out` gets the
+    complete output on every rank."""
+    stream = kw.pop("stream", None)
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    keep = {"num_kv_heads": num_kv_heads}
+    p = _decode_params(q, k_cache, v_cache, out, layout, kw.get("seq_lens"),
+                       kw.get("seq_lens_dev"), kw.get("block_table"), kw.get("fixed_block", 0),
+                       kw.get("workspace"), kw.get("split_keys", 0), kw.get("max_ctas", 0),
+                       kw.get("plan_len_hint", 0), kw.get("status"), stream, keep,
+                       kw.get("early_prefetch", False))
+    _check(lib().gqa_decode_seqpar(C.byref(p), comm._h), "gqa_decode_seqpar")
 
 
 def oproj_workspace(hidden: int, num_kv_heads: int, device) -> Optional[torch.Tensor]:

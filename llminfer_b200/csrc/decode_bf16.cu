@@ -380,7 +380,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
         }
         __syncthreads();
         {
-            const bool final_out = (it.nsplits == 1);
+            const bool final_out = (it.nsplits == 1) && a.always_partial == 0;
             float* rec = a.workspace + (int64_t)item * group * (kHeadDim + 2);
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out) +
                 ((int64_t)it.b * a.num_q_heads + (int64_t)it.hk * group) * kHeadDim;

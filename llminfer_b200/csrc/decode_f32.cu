@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
         }
         __syncthreads();
         {
-            const bool final_out = (it.nsplits == 1);
+            const bool final_out = (it.nsplits == 1) && a.always_partial == 0;
             float* rec = a.workspace + (int64_t)item * group * (kHeadDim + 2);
             float* out = reinterpret_cast<float*>(a.out) +
                 ((int64_t)it.b * a.num_q_heads + (int64_t)it.hk * group) * kHeadDim;
@@ -199,6 +199,9 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
     }
 }
 
+constexpr int kCombineLocal = 0;   // merge the splits of a unit
+constexpr int kCombineGather = 1;  // ... and exchange the finished rows (KV-head-parallel)
+constexpr int kCombineSeqPar = 2;  // ... and merge with the other ranks' slices of the keys
 constexpr int kCombineWideGrid = 160;  // largest grid that runs with 4 lanes per channel
 constexpr int kCombineTile = 32;   // splits merged per pass
 constexpr int kCombineSlots = 8;   // partial sums per channel per pass, whatever the CTA width
@@ -221,7 +224,7 @@ constexpr int kCombineSlots = 8;   // partial sums per channel per pass, whateve
 // soon as it is merged, so the transfer of the first rows overlaps the merge of the others and
 // the separate gather launch goes away. Units that were not split are pushed from the output
 // the streaming kernel wrote. Used only when every CTA of the grid is resident at once.
-template <bool BF16_OUT, int LANES, bool GATHER>
+template <bool BF16_OUT, int LANES, int MODE>
 __global__ void __launch_bounds__(kHeadDim * LANES)
     gqa_decode_combine(const DecodeArgs a, const PeerGatherArgs g) {
     constexpr int kOwn = kCombineSlots / LANES;            // slots per thread
@@ -243,20 +246,20 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
     int32_t first, nsplits;
     unit_items(a, tables, b, hk, &first, &nsplits);
     // Not split: the streaming kernel already wrote the final output.
-    if (!GATHER && nsplits <= 1) return;
+    if (MODE == kCombineLocal && nsplits <= 1) return;
 
     const int d = threadIdx.x & (kHeadDim - 1);
     const int j = threadIdx.x >> 7;
     const int64_t o_idx = ((int64_t)b * a.num_q_heads + h) * kHeadDim + d;
     float result = 0.f;  // the finished channel, held by the threads with j == 0
-    if (nsplits > 1) {
+    float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
+    if (nsplits > 1 || MODE == kCombineSeqPar) {
         const int64_t rec_floats = (int64_t)group * (kHeadDim + 2);
         const float* rec0 = a.workspace + (int64_t)first * rec_floats;
         const float* m_base = rec0 + group * kHeadDim + n;
         const float* l_base = m_base + group;
         const float* o_base = rec0 + n * kHeadDim + d;
 
-        float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
         for (int32_t base = 0; base < nsplits; base += kCombineTile) {
             const int32_t cnt = min(kCombineTile, nsplits - base);
             float o[kOwn][kPerSlot];
@@ -321,7 +324,7 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
             __syncthreads();  // the next pass overwrites s_m, s_l and s_part
         }
         timeline_mark(7, a.fixed_block);
-        if (j == 0) {
+        if (j == 0 && MODE != kCombineSeqPar) {
             result = acc / l_run;
             if (BF16_OUT) {
                 reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(result);
@@ -329,53 +332,111 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
                 reinterpret_cast<float*>(a.out)[o_idx] = result;
             }
         }
-    } else if (GATHER && j == 0) {
+    } else if (MODE == kCombineGather && j == 0) {
         result = BF16_OUT ? __bfloat162float(__ldcg(reinterpret_cast<const __nv_bfloat16*>(a.out) + o_idx))
                           : __ldcg(reinterpret_cast<const float*>(a.out) + o_idx);
     }
-    if (!GATHER) return;
+    if (MODE == kCombineLocal) return;
 
-    // ---- exchange of the row with the other ranks ----
-    constexpr int kRowWords = BF16_OUT ? kHeadDim / 2 : kHeadDim;
-    __shared__ uint32_t s_row[kRowWords];
+    // ---- exchange with the other ranks ----
     __shared__ uint32_t s_step;
     __shared__ int s_timed_out;
     uint8_t* mine = g.windows[g.rank];
     WindowCtrl* ctrl = window_ctrl(mine, g.slot_bytes, g.nranks);
-    if (j == 0) {
-        if (BF16_OUT) {
-            const uint32_t bits = __bfloat16_as_ushort(__float2bfloat16(result));
-            const uint32_t next = __shfl_down_sync(0xffffffffu, bits, 1);
-            if ((d & 1) == 0) s_row[d >> 1] = bits | (next << 16);
-        } else {
-            s_row[d] = __float_as_uint(result);
-        }
-    }
     if (threadIdx.x == 0) {
         s_step = *reinterpret_cast<volatile uint32_t*>(&ctrl->step) + 1;
         s_timed_out = 0;
     }
-    __syncthreads();
-    const uint32_t step = s_step;
-    const uint64_t row_off = (uint64_t)blockIdx.x * kRowWords;
-    const int total = kRowWords * g.nranks;
-    for (int i = threadIdx.x; i < total; i += kHeadDim * LANES) {
-        const int p = i / kRowWords;
-        const int w = i - p * kRowWords;
-        push_word(window_slot(g.windows[p], step, g.nranks, g.rank, g.slot_bytes) + row_off + w,
-                  step, s_row[w]);
-    }
-    const unsigned long long start = global_timer();
     bool timed_out = false;
-    for (int i = threadIdx.x; i < total && !timed_out; i += kHeadDim * LANES) {
-        const int p = i / kRowWords;
-        const int w = i - p * kRowWords;
-        uint32_t data;
-        if (poll_word(window_slot(mine, step, g.nranks, p, g.slot_bytes) + row_off + w, step,
-                      start, &data)) {
-            g.recv[(uint64_t)p * g.words + row_off + w] = data;
-        } else {
-            timed_out = true;
+    if (MODE == kCombineGather) {
+        // The finished row goes to every rank and the same row of every rank comes back.
+        constexpr int kRowWords = BF16_OUT ? kHeadDim / 2 : kHeadDim;
+        __shared__ uint32_t s_row[kRowWords];
+        if (j == 0) {
+            if (BF16_OUT) {
+                const uint32_t bits = __bfloat16_as_ushort(__float2bfloat16(result));
+                const uint32_t next = __shfl_down_sync(0xffffffffu, bits, 1);
+                if ((d & 1) == 0) s_row[d >> 1] = bits | (next << 16);
+            } else {
+                s_row[d] = __float_as_uint(result);
+            }
+        }
+        __syncthreads();
+        const uint32_t step = s_step;
+        const uint64_t row_off = (uint64_t)blockIdx.x * kRowWords;
+        const int total = kRowWords * g.nranks;
+        for (int i = threadIdx.x; i < total; i += kHeadDim * LANES) {
+            const int p = i / kRowWords;
+            const int w = i - p * kRowWords;
+            push_word(window_slot(g.windows[p], step, g.nranks, g.rank, g.slot_bytes) + row_off + w,
+                      step, s_row[w]);
+        }
+        const unsigned long long start = global_timer();
+        for (int i = threadIdx.x; i < total && !timed_out; i += kHeadDim * LANES) {
+            const int p = i / kRowWords;
+            const int w = i - p * kRowWords;
+            uint32_t data;
+            if (poll_word(window_slot(mine, step, g.nranks, p, g.slot_bytes) + row_off + w, step,
+                          start, &data)) {
+                g.recv[(uint64_t)p * g.words + row_off + w] = data;
+            } else {
+                timed_out = true;
+            }
+        }
+    } else {
+        // Sequence-parallel: this rank saw a slice of the row's keys. Its record (128 channel
+        // sums relative to its maximum, the maximum, the row sum) goes to every other rank; the
+        // records of all ranks are merged in rank order, so every rank gets the same bits.
+        constexpr int kRecWords = kHeadDim + 2;
+        __shared__ uint32_t s_rec[kMaxPeers][kRecWords];
+        if (j == 0) s_rec[g.rank][d] = __float_as_uint(acc);
+        if (threadIdx.x == 0) {
+            s_rec[g.rank][kHeadDim] = __float_as_uint(m_run);
+            s_rec[g.rank][kHeadDim + 1] = __float_as_uint(l_run);
+        }
+        __syncthreads();
+        const uint32_t step = s_step;
+        const uint64_t row_off = (uint64_t)blockIdx.x * kRecWords;
+        const int total = kRecWords * g.nranks;
+        for (int i = threadIdx.x; i < total; i += kHeadDim * LANES) {
+            const int p = i / kRecWords;
+            const int w = i - p * kRecWords;
+            if (p == g.rank) continue;
+            push_word(window_slot(g.windows[p], step, g.nranks, g.rank, g.slot_bytes) + row_off + w,
+                      step, s_rec[g.rank][w]);
+        }
+        const unsigned long long start = global_timer();
+        for (int i = threadIdx.x; i < total && !timed_out; i += kHeadDim * LANES) {
+            const int p = i / kRecWords;
+            const int w = i - p * kRecWords;
+            if (p == g.rank) continue;
+            uint32_t data;
+            if (poll_word(window_slot(mine, step, g.nranks, p, g.slot_bytes) + row_off + w, step,
+                          start, &data)) {
+                s_rec[p][w] = data;
+            } else {
+                timed_out = true;
+            }
+        }
+        if (timed_out) s_timed_out = 1;
+        __syncthreads();
+        if (j == 0 && s_timed_out == 0) {
+            float m_all = __uint_as_float(s_rec[0][kHeadDim]);
+            for (int r = 1; r < g.nranks; ++r) {
+                m_all = fmaxf(m_all, __uint_as_float(s_rec[r][kHeadDim]));
+            }
+            float l_all = 0.f, o_all = 0.f;
+            for (int r = 0; r < g.nranks; ++r) {
+                const float diff = __uint_as_float(s_rec[r][kHeadDim]) - m_all;
+                const float w = BF16_OUT ? ex2_approx(diff) : exp2f(diff);
+                l_all += __uint_as_float(s_rec[r][kHeadDim + 1]) * w;
+                o_all += __uint_as_float(s_rec[r][d]) * w;
+            }
+            if (BF16_OUT) {
+                reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(o_all / l_all);
+            } else {
+                reinterpret_cast<float*>(a.out)[o_idx] = o_all / l_all;
+            }
         }
     }
     if (timed_out) s_timed_out = 1;
@@ -390,7 +451,7 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
         const uint32_t ticket = atomicAdd(&ctrl->ticket_out, 1u);
         if (ticket == gridDim.x - 1) {
             ctrl->ticket_out = 0;
-            ctrl->step = step;
+            ctrl->step = s_step;
         }
     }
 }
@@ -407,31 +468,31 @@ cudaError_t launch_stream_f32(const DecodeArgs& args, int grid, cudaStream_t str
 }
 
 cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t stream,
-                           const PeerGatherArgs* gather) {
+                           const PeerGatherArgs* gather, bool sequence_parallel) {
     const size_t smem =
         args.seq_lens_dev != nullptr ? 2 * ((size_t)args.batch + 1) * sizeof(int32_t) : 0;
     const int grid = args.batch * args.num_q_heads;
     const bool wide = grid <= kCombineWideGrid;
     PeerGatherArgs g;
     std::memset(&g, 0, sizeof(g));
+    if (gather != nullptr) g = *gather;
+    const dim3 block(kHeadDim * (wide ? 4 : 2));
+#define GQA_COMBINE(MODE)                                                                       \
+    (bf16_out ? (wide ? launch_pdl(gqa_decode_combine<true, 4, MODE>, dim3(grid), block, smem,  \
+                                   stream, args, g)                                             \
+                      : launch_pdl(gqa_decode_combine<true, 2, MODE>, dim3(grid), block, smem,  \
+                                   stream, args, g))                                            \
+              : (wide ? launch_pdl(gqa_decode_combine<false, 4, MODE>, dim3(grid), block, smem, \
+                                   stream, args, g)                                             \
+                      : launch_pdl(gqa_decode_combine<false, 2, MODE>, dim3(grid), block, smem, \
+                                   stream, args, g)))
+    if (gather != nullptr && sequence_parallel) return GQA_COMBINE(kCombineSeqPar);
     if (gather != nullptr) {
         if (!wide) return cudaErrorInvalidValue;  // the caller checks combine_can_gather()
-        g = *gather;
-        return bf16_out ? launch_pdl(gqa_decode_combine<true, 4, true>, dim3(grid),
-                                     dim3(kHeadDim * 4), smem, stream, args, g)
-                        : launch_pdl(gqa_decode_combine<false, 4, true>, dim3(grid),
-                                     dim3(kHeadDim * 4), smem, stream, args, g);
+        return GQA_COMBINE(kCombineGather);
     }
-    if (bf16_out) {
-        return wide ? launch_pdl(gqa_decode_combine<true, 4, false>, dim3(grid),
-                                 dim3(kHeadDim * 4), smem, stream, args, g)
-                    : launch_pdl(gqa_decode_combine<true, 2, false>, dim3(grid),
-                                 dim3(kHeadDim * 2), smem, stream, args, g);
-    }
-    return wide ? launch_pdl(gqa_decode_combine<false, 4, false>, dim3(grid), dim3(kHeadDim * 4),
-                             smem, stream, args, g)
-                : launch_pdl(gqa_decode_combine<false, 2, false>, dim3(grid), dim3(kHeadDim * 2),
-                             smem, stream, args, g);
+    return GQA_COMBINE(kCombineLocal);
+#undef GQA_COMBINE
 }
 
 bool combine_can_gather(int batch, int num_q_heads, int sm_count) {

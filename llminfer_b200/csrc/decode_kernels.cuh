@@ -36,13 +36,21 @@ struct PeerGatherArgs;
 // One CTA per (sequence, query head); merges the partial records of split units. With
 // `gather` the same kernel also exchanges the finished rows with the other ranks of a
 // KV-head-parallel node through their peer windows (allowed when combine_can_gather()).
+// With `sequence_parallel` (and `gather`) the rows are instead merged with the records the
+// other ranks computed on their slices of the keys.
 cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t stream,
-                           const PeerGatherArgs* gather = nullptr);
+                           const PeerGatherArgs* gather = nullptr,
+                           bool sequence_parallel = false);
 bool combine_can_gather(int batch, int num_q_heads, int sm_count);
 
 // gqa_decode with the gather fused into the combine kernel when that is possible; *fused
 // tells whether it was (if not, nothing was exchanged and the caller gathers separately).
 int decode_with_gather(const gqa_decode_params* p, const PeerGatherArgs* gather, bool* fused);
+
+// Sequence-parallel decode: p describes this rank's slice of every sequence (all heads); the
+// combine kernel merges the ranks' records through the peer windows and writes the complete
+// output on every rank.
+int decode_sequence_parallel(const gqa_decode_params* p, const PeerGatherArgs* gather);
 
 // Tensor map of a row-major BF16 matrix [rows][cols] with `pitch` elements between rows, boxes
 // of 16 rows x 64 columns in 128-byte swizzled rows (cached: weights keep their address).

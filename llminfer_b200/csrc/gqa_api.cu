@@ -382,6 +382,11 @@ gqa_kv_layout clean_layout(const gqa_kv_layout& l) {
 
 }  // namespace
 
+namespace {
+int decode_impl(const gqa_decode_params* p, const gqa::PeerGatherArgs* gather,
+                bool sequence_parallel, bool* fused);
+}  // namespace
+
 int gqa::cached_matrix_map(const void* base, int64_t cols, int64_t rows, int64_t pitch,
                            CUtensorMap* map) {
     struct Entry {
@@ -496,6 +501,18 @@ int gqa_decode(const gqa_decode_params* p) { return gqa::decode_with_gather(p, n
 
 int gqa::decode_with_gather(const gqa_decode_params* p, const gqa::PeerGatherArgs* gather,
                             bool* fused) {
+    return decode_impl(p, gather, false, fused);
+}
+
+int gqa::decode_sequence_parallel(const gqa_decode_params* p, const gqa::PeerGatherArgs* gather) {
+    if (gather == nullptr) return GQA_ERR_NULL;
+    return decode_impl(p, gather, true, nullptr);
+}
+
+namespace {
+
+int decode_impl(const gqa_decode_params* p, const gqa::PeerGatherArgs* gather,
+                bool sequence_parallel, bool* fused) {
     if (fused != nullptr) *fused = false;
     int rc = validate_decode(p);
     if (rc != GQA_OK) return rc;
@@ -505,6 +522,12 @@ int gqa::decode_with_gather(const gqa_decode_params* p, const gqa::PeerGatherArg
     gqa_decode_plan_info plan;
     rc = plan_from_params(p, sms, &plan);
     if (rc != GQA_OK) return rc;
+    if (sequence_parallel && !plan.needs_combine) {
+        // Every unit leaves a record for the merge across ranks, also when it is not split.
+        plan.needs_combine = 1;
+        plan.workspace_bytes = (size_t)plan.num_items * (p->num_q_heads / p->num_kv_heads) *
+                               (kHeadDim + 2) * sizeof(float);
+    }
     if (plan.needs_combine) {
         if (p->workspace == nullptr) return GQA_ERR_NULL;
         if (p->workspace_bytes < plan.workspace_bytes) return GQA_ERR_WORKSPACE;
@@ -534,6 +557,7 @@ int gqa::decode_with_gather(const gqa_decode_params* p, const gqa::PeerGatherArg
     a.block_tokens = p->layout.block_tokens;
     a.fixed_block = p->fixed_block;
     a.early_prefetch = p->early_prefetch ? 1 : 0;
+    a.always_partial = sequence_parallel ? 1 : 0;
     a.scale_log2 = (1.0f / sqrtf((float)kHeadDim)) * 1.44269504088896340736f;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(p->stream);
 
@@ -554,14 +578,17 @@ int gqa::decode_with_gather(const gqa_decode_params* p, const gqa::PeerGatherArg
     }
     if (e != cudaSuccess) return GQA_ERR_CUDA;
     if (plan.needs_combine) {
-        const bool fuse =
-            gather != nullptr && gqa::combine_can_gather(p->batch, p->num_q_heads, sms);
-        e = gqa::launch_combine(a, p->dtype == GQA_DTYPE_BF16, stream, fuse ? gather : nullptr);
+        const bool fuse = sequence_parallel || (gather != nullptr && gqa::combine_can_gather(
+                                                    p->batch, p->num_q_heads, sms));
+        e = gqa::launch_combine(a, p->dtype == GQA_DTYPE_BF16, stream, fuse ? gather : nullptr,
+                                sequence_parallel);
         if (e != cudaSuccess) return GQA_ERR_CUDA;
         if (fused != nullptr) *fused = fuse;
     }
     return GQA_OK;
 }
+
+}  // namespace
 
 extern "C" {
 

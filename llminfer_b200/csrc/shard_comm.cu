@@ -364,4 +364,15 @@ int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathere
     return gqa_comm_all_gather(comm, p->out, gathered, bytes, p->stream);
 }
 
+int gqa_decode_seqpar(const gqa_decode_params* p, gqa_comm* comm) {
+    if (p == nullptr || comm == nullptr) return GQA_ERR_NULL;
+    if (p->batch <= 0 || p->num_q_heads <= 0 || p->head_dim <= 0) return GQA_ERR_SHAPE;
+    if (comm->window_local == nullptr) return GQA_ERR_COMM;
+    // One record per (sequence, query head) and rank: 128 channel sums, maximum, row sum.
+    const size_t bytes = (size_t)p->batch * p->num_q_heads * (p->head_dim + 2) * sizeof(float);
+    if (2 * bytes > comm->slot_bytes) return GQA_ERR_SHAPE;
+    const PeerGatherArgs g = gather_args(comm, nullptr, nullptr, bytes, p->status_dev);
+    return gqa::decode_sequence_parallel(p, &g);
+}
+
 }  // extern "C"

@@ -41,6 +41,7 @@ struct DecodeArgs {
     int32_t fixed_block;
     int32_t head_before_token;  // order of the middle tensor-map coordinates (BF16 path)
     int32_t early_prefetch;     // K/V stages may be requested before the predecessor is done
+    int32_t always_partial;     // every item leaves a partial record, even a unit's only one
     float scale_log2;  // (1 / sqrt(head_dim)) * log2(e)
 };
 

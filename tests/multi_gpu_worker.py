@@ -109,7 +109,7 @@ def main() -> None:
 
     # The same through the NVLink peer-store gather, step after step (the two window halves
     # alternate) and inside a replayed CUDA graph (the step counter lives on the device).
-    comm.enable_peer_gather(max(batch * per_q * d * 2, 4 * per_kv * 3 * 256))
+    comm.enable_peer_gather(max(batch * per_q * d * 2, 4 * per_kv * 3 * 256, batch * hq * (d + 2) * 4))
     for _ in range(5):
         again = run(q_l, k_l, v_l, per_q, per_kv, sharded=True)
         assert torch.equal(again.view(torch.int16), full.view(torch.int16)), "peer gather != unsharded"
@@ -181,6 +181,42 @@ def main() -> None:
         assert torch.equal(got_res.view(torch.int16), want_res.view(torch.int16)), "sharded o-proj"
     want_np = oracle.gemv_add(attn.reshape(tokens, -1), w_o, res0, accum=1)
     assert not H.bf16_mismatches(H.bits_of(got_res), want_np).any()
+
+    # Sequence-parallel: every rank holds all heads and every world-th block of each sequence;
+    # the combine kernel merges the ranks' records. Every rank gets the same bits, and they
+    # agree with the oracle on the whole sequences.
+    sp_lens = [3000, 2100, 2048]
+    nblk = [-(-n // block_tokens) for n in sp_lens]
+    local_tab = np.zeros((batch, blocks_per_seq), dtype=np.int32)
+    local_lens = []
+    for b in range(batch):
+        mine = list(range(rank, nblk[b], world))
+        local_tab[b, :len(mine)] = table[b, mine]
+        keys = sum(min(block_tokens, sp_lens[b] - i * block_tokens) for i in mine)
+        assert keys >= 1
+        local_lens.append(keys)
+    layout_sp = gqa.layout_pool(num_blocks, block_tokens, hkv)
+    dq_sp, dk_sp, dv_sp = H.bf16_tensor(q, dev), H.bf16_tensor(k_pool, dev), H.bf16_tensor(v_pool, dev)
+    ws_sp = gqa.binding.workspace_for(batch, hq, hkv, dev)
+    for split_keys in (0, 512):
+        out_sp = torch.zeros(batch, hq, d, dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            gqa.decode_seqpar(comm, dq_sp, dk_sp, dv_sp, out_sp, num_kv_heads=hkv, layout=layout_sp,
+                              seq_lens=local_lens,
+                              seq_lens_dev=torch.tensor(local_lens, dtype=torch.int32, device=dev),
+                              block_table=torch.from_numpy(local_tab).to(dev), workspace=ws_sp,
+                              split_keys=split_keys, status=status)
+            torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        want_sp = oracle.gqa_decode(q, k_pool.reshape(-1), v_pool.reshape(-1), sp_lens, hkv=hkv,
+                                    stride_block=hkv * block_tokens * d, stride_token=d,
+                                    stride_head=block_tokens * d, block_tokens=block_tokens,
+                                    block_table=table)
+        abs_err, rel_err = H.errors(out_sp.float().cpu().numpy(), want_sp)
+        assert abs_err <= 2e-2 and rel_err <= 1e-2, ("sequence-parallel", split_keys, abs_err, rel_err)
+        sp_bits = [None] * world
+        dist.all_gather_object(sp_bits, H.bits_of(out_sp).tobytes())
+        assert all(x == sp_bits[0] for x in sp_bits), "ranks disagree on the merged output"
 
     # The host-buffer step with the gather inside.
     layout_l = gqa.layout_pool(num_blocks, block_tokens, per_kv)
