@@ -260,7 +260,7 @@ def run_ours(args) -> None:
             # Needs CUDA IPC between the ranks' processes; every rank falls back to NCCL
             # together if any of them cannot set it up.
             try:
-                comm.enable_peer_gather(1 << 20)
+                comm.enable_peer_gather(4 << 20)
                 ok = 1
             except gqa.GqaError:
                 ok = 0
@@ -272,8 +272,16 @@ def run_ours(args) -> None:
 
     hq_total, hkv_total, lens, layout_kind, dtype_name = WORKLOADS[args.workload]
     batch = len(lens)
-    shard = gqa.shard_plan(hq_total, hkv_total, world, rank)
-    hq, hkv = shard["num_local_q_heads"], shard["num_local_kv_heads"]
+    seq_parallel = args.partition == "sequence" and world > 1
+    if seq_parallel:
+        # Every rank holds all heads and 1/world of every sequence's keys (whole chunks).
+        if not args.attn_only or args.gather != "peer":
+            raise SystemExit("--partition sequence needs --attn-only and the peer windows")
+        hq, hkv = hq_total, hkv_total
+        lens = [max(32, l // world // 32 * 32) for l in lens]
+    else:
+        shard = gqa.shard_plan(hq_total, hkv_total, world, rank)
+        hq, hkv = shard["num_local_q_heads"], shard["num_local_kv_heads"]
     tdtype = torch.bfloat16 if dtype_name == "bf16" else torch.float32
     elem = 2 if dtype_name == "bf16" else 4
     gen = torch.Generator(device=dev)
@@ -353,6 +361,8 @@ def run_ours(args) -> None:
         q_in = q_rot if has_front else q_raw
         if comm is None:
             gqa.decode(q_in, k_pool, v_pool, out, **kw)
+        elif seq_parallel:
+            gqa.decode_seqpar(comm, q_in, k_pool, v_pool, out, **kw)
         else:
             gqa.decode_sharded(comm, gathered, q_in, k_pool, v_pool, out, **kw)
 
@@ -418,7 +428,7 @@ def run_ours(args) -> None:
     # L2 holds; sharded runs exchange the per-KV-head sums through the peer windows.
     oproj_info = None
     qkv_info = None
-    if dtype_name == "bf16" and (comm is None or args.gather == "peer"):
+    if dtype_name == "bf16" and (comm is None or args.gather == "peer") and not seq_parallel:
         hidden = HIDDEN[args.workload.split("-bf16")[0]]
         weight_bytes = hidden * hq * HEAD_DIM * 2
         copies = max(2, -(-(256 << 20) // weight_bytes))
@@ -585,6 +595,8 @@ def main() -> None:
     ap.add_argument("--workload", choices=tuple(WORKLOADS), default=DEFAULT_WORKLOAD)
     ap.add_argument("--gather", choices=("peer", "nccl"), default="peer",
                     help="N > 1: gather the output with peer stores over NVLink or with NCCL")
+    ap.add_argument("--partition", choices=("heads", "sequence"), default="heads",
+                    help="N > 1: KV heads per GPU (default) or a slice of every sequence per GPU")
     ap.add_argument("--sweep", action="store_true",
                     help="N = 1: also time the attention kernels on the other workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
