@@ -186,15 +186,8 @@ def main() -> None:
     # the combine kernel merges the ranks' records. Every rank gets the same bits, and they
     # agree with the oracle on the whole sequences.
     sp_lens = [3000, 2100, 2048]
-    nblk = [-(-n // block_tokens) for n in sp_lens]
-    local_tab = np.zeros((batch, blocks_per_seq), dtype=np.int32)
-    local_lens = []
-    for b in range(batch):
-        mine = list(range(rank, nblk[b], world))
-        local_tab[b, :len(mine)] = table[b, mine]
-        keys = sum(min(block_tokens, sp_lens[b] - i * block_tokens) for i in mine)
-        assert keys >= 1
-        local_lens.append(keys)
+    local_rows, local_lens = sharding.sequence_slice(sp_lens, table, block_tokens, world, rank)
+    local_tab = np.array(local_rows, dtype=np.int32)
     layout_sp = gqa.layout_pool(num_blocks, block_tokens, hkv)
     dq_sp, dk_sp, dv_sp = H.bf16_tensor(q, dev), H.bf16_tensor(k_pool, dev), H.bf16_tensor(v_pool, dev)
     ws_sp = gqa.binding.workspace_for(batch, hq, hkv, dev)

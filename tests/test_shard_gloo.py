@@ -14,6 +14,7 @@ for _p in (_ROOT, _ROOT / "tests", _ROOT / "tests" / "golden"):
         sys.path.insert(0, str(_p))
 
 import numpy as np
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -77,3 +78,31 @@ def test_head_parallel_gather_reassembles_the_full_output(built_lib):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert results == {0: True, 1: True}
+
+
+def test_sequence_slices_partition_every_sequence(built_lib):
+    """Block-interleaved slices for the sequence-parallel decode: over all ranks every key is
+    held exactly once, only a rank's last block can be partly filled, and a rank without keys
+    is refused."""
+    from llminfer_b200 import sharding
+    block_tokens, lens = 256, [3000, 2100, 2048, 257]
+    table = [[100 * b + i for i in range(12)] for b in range(len(lens))]
+    for nranks in (1, 2, 4):
+        if nranks > 2:
+            lens_n, table_n = lens[:3], table[:3]  # the 257-key sequence has only two blocks
+        else:
+            lens_n, table_n = lens, table
+        seen = [[] for _ in lens_n]
+        total = [0] * len(lens_n)
+        for rank in range(nranks):
+            rows, local = sharding.sequence_slice(lens_n, table_n, block_tokens, nranks, rank)
+            for b, (row, keys) in enumerate(zip(rows, local)):
+                held = -(-keys // block_tokens)
+                assert len(row) == 12 and all(v == 0 for v in row[held:])
+                seen[b] += row[:held]
+                total[b] += keys
+        assert total == lens_n
+        for b, length in enumerate(lens_n):
+            assert sorted(seen[b]) == table_n[b][:-(-length // block_tokens)]
+    with pytest.raises(ValueError):
+        sharding.sequence_slice([257], [table[0]], block_tokens, 4, 3)
