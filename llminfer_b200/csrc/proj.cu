@@ -1,4 +1,5 @@
-// Output projection with residual add behind decode attention; see include/gqa_b200.h.
+// The projections on either side of decode attention: output projection with residual add
+// behind it, packed QKV projection in front of it (one kernel); see include/gqa_b200.h.
 //
 // Takes the place of fused_gemv_add_bf16x8_kernel
 // (code/source/op/kernel/cuda/matmul_kernel.cu:143-170): residual[n] += dot(x, W[n]). There one
@@ -434,17 +435,25 @@ int run(const gqa_oproj_params* p, const SplitOut* split, gqa_comm* comm) {
     }
     const int grid = (workers + warps - 1) / warps * groups;
     const size_t smem = smem_bytes(warps, stages, per_group);
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(oproj_residual_kernel<false>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
-        if (attr_err == cudaSuccess) {
-            attr_err = cudaFuncSetAttribute(oproj_residual_kernel<true>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    // The shared-memory limit is a per-device property of the kernels: raise it once per device.
+    {
+        static std::mutex mu;
+        static bool raised[64] = {};
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64) return GQA_ERR_CUDA;
+        if (!raised[dev]) {
+            if (cudaFuncSetAttribute(oproj_residual_kernel<false>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kMaxSmem) != cudaSuccess ||
+                cudaFuncSetAttribute(oproj_residual_kernel<true>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kMaxSmem) != cudaSuccess) {
+                return GQA_ERR_CUDA;
+            }
+            raised[dev] = true;
         }
-    });
-    if (attr_err != cudaSuccess || smem > (size_t)kMaxSmem) return GQA_ERR_CUDA;
+    }
+    if (smem > (size_t)kMaxSmem) return GQA_ERR_SHAPE;
     CUtensorMap wmap;
     const int mrc = cached_matrix_map(p->weight, (int64_t)p->num_q_heads * kHeadDim, p->hidden,
                                       p->weight_ld, &wmap);

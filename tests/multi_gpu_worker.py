@@ -211,6 +211,22 @@ def main() -> None:
         dist.all_gather_object(sp_bits, H.bits_of(out_sp).tobytes())
         assert all(x == sp_bits[0] for x in sp_bits), "ranks disagree on the merged output"
 
+    # The same in FP32 on contiguous parts of a reference-layout cache (the narrow combine grid
+    # takes the kernel's other width).
+    part = len32 // world
+    sl = slice(rank * part, (rank + 1) * part)
+    out_sp32 = torch.zeros(1, hq32, d, dtype=torch.float32, device=dev)
+    gqa.decode_seqpar(comm, q32, k32[:, sl].contiguous(), v32[:, sl].contiguous(), out_sp32,
+                      num_kv_heads=hkv32, layout=gqa.layout_reference(1, part, hkv32),
+                      seq_lens=[part], workspace=ws32, split_keys=32, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    rel32 = ((out_sp32 - full32).abs().max() / full32.abs().max()).item()
+    assert rel32 <= 1e-5, rel32
+    sp32_bits = [None] * world
+    dist.all_gather_object(sp32_bits, out_sp32.cpu().numpy().tobytes())
+    assert all(x == sp32_bits[0] for x in sp32_bits), "ranks disagree on the FP32 merged output"
+
     # The host-buffer step with the gather inside.
     layout_l = gqa.layout_pool(num_blocks, block_tokens, per_kv)
     session = gqa.Session(batch, per_q, per_kv, blocks_per_seq * block_tokens)
