@@ -92,6 +92,32 @@ def test_compute_entry_points_reject_bad_arguments_before_touching_the_device(gq
     assert handle.gqa_session_create(2, 1, 32, 8, 64, 64, C.byref(out)) == -3
 
 
+def test_binding_structs_match_the_header_layout(gqa, tmp_path):
+    """The ctypes mirrors of the parameter structs have the size and field offsets the C
+    compiler gives the declarations in include/gqa_b200.h."""
+    import subprocess
+    from llminfer_b200 import binding as B
+    mirrors = {"gqa_kv_layout": B._Layout, "gqa_decode_params": B._DecodeParams,
+               "gqa_decode_plan_info": B._PlanInfo, "gqa_front_params": B._FrontParams,
+               "gqa_oproj_params": B._OprojParams, "gqa_qkv_params": B._QkvParams}
+    lines = ["#include <stddef.h>", "#include <stdio.h>", '#include "gqa_b200.h"', "int main(void) {"]
+    for name, mirror in mirrors.items():
+        lines.append(f'printf("{name} %zu\\n", sizeof({name}));')
+        for field, _ in mirror._fields_:
+            lines.append(f'printf("{name}.{field} %zu\\n", offsetof({name}, {field}));')
+    lines += ["return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout
+    got = dict(line.split() for line in out.strip().splitlines())
+    for name, mirror in mirrors.items():
+        assert int(got[name]) == C.sizeof(mirror), name
+        for field, _ in mirror._fields_:
+            assert int(got[f"{name}.{field}"]) == getattr(mirror, field).offset, (name, field)
+
+
 def test_projection_entry_points_validate_on_the_host(gqa):
     """Workspace sizes are pure functions; bad shapes and missing buffers are refused before
     any CUDA call (device pointers here are fake, non-null and aligned)."""
