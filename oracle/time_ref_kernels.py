@@ -2,7 +2,7 @@
 (oracle/_ref/libref_attn.so, built by oracle/build_ref.sh for sm_100) on the GPU of this
 machine, for the BASELINE configurations they can run: BF16, head_dim 128, one sequence (one
 token for the projection), contiguous cache. TEST INFRASTRUCTURE: the
-numbers go into the comparison table of BASELINE.md; nothing of the product uses this file.
+numbers are reference points for comparison tables; nothing of the product uses this file.
 
 usage: python oracle/time_ref_kernels.py
 """
