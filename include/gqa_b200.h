@@ -423,7 +423,9 @@ typedef struct gqa_oproj_params {
  * head). The caller zero-fills it once after allocating it; every call leaves it zeroed
  * where that matters (per-tile arrival counters), so it can be reused by the next call on
  * the same stream without further care. Calls that overlap on different streams need
- * workspaces of their own.
+ * workspaces of their own. Sums in flight are tagged with a 32-bit launch counter kept in the
+ * workspace: a process that makes more than 2^31 calls on one workspace should zero-fill it
+ * again (between calls) before the counter wraps.
  */
 size_t gqa_oproj_workspace_bytes(int32_t hidden, int32_t num_kv_heads);
 
