@@ -330,7 +330,11 @@ int gqa_comm_all_gather(gqa_comm* comm, const void* send, void* recv, size_t byt
  * 4 * nranks * max_bytes_per_rank bytes that the other ranks map through CUDA IPC (one process
  * per GPU on one node, all GPUs visible to every process). Afterwards gqa_decode_sharded
  * gathers with the GPUs' own stores (gqa_comm_peer_gather) whenever the output fits, instead
- * of ncclAllGather. Synchronises the device. At most 8 ranks.
+ * of ncclAllGather. Synchronises the device. At most 8 ranks. The same windows carry the
+ * exchanges of gqa_oproj_residual_sharded and gqa_decode_seqpar. Words in a window are tagged
+ * with a 32-bit step counter kept on the device: a process that runs more than 2^31 exchange
+ * steps on one communicator should disable and enable the peer gather again (between steps,
+ * on every rank) before the counter wraps.
  */
 int gqa_comm_enable_peer_gather(gqa_comm* comm, size_t max_bytes_per_rank);
 /* Back to ncclAllGather (every rank must do the same); frees the window. */
