@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define GQA_B200_ABI_VERSION 1
+#define GQA_B200_ABI_VERSION 2
 
 /* ---- status codes ------------------------------------------------------------------- */
 #define GQA_OK 0
@@ -37,6 +37,16 @@ extern "C" {
 #define GQA_ERR_COMM (-9)        /* NCCL is missing or a collective failed */
 #define GQA_ERR_POOL (-10)       /* KV pool: out of blocks, bad sequence or handle */
 #define GQA_ERR_TIMEOUT (-11)    /* a bounded device wait ran out (see status word) */
+
+/*
+ * Values a kernel leaves in the caller's device status word (status_dev; 0 = nothing happened).
+ * The kernels never trap, fault or hang on bad device-side input: they clamp or skip and say so.
+ */
+#define GQA_STATUS_STAGE_TIMEOUT 1 /* a staged K/V chunk did not arrive within two seconds */
+#define GQA_STATUS_PEER_TIMEOUT 2  /* another rank's (or CTA's) words did not arrive in time */
+#define GQA_STATUS_BAD_INPUT 3     /* a length, position or block id read from device memory was
+                                      out of range (clamped / row skipped), or split partials did
+                                      not fit the workspace (those units are left unwritten) */
 
 /* dtype values are the reference's base::DataType values (code/include/base/base.h:51-58). */
 #define GQA_DTYPE_F32 1
@@ -81,14 +91,30 @@ int gqa_layout_pool(int32_t num_blocks, int32_t block_tokens, int32_t num_kv_hea
  * (:44-208 single pass, :210-388 KV split, :399-438 combine), generalised to a batch of
  * sequences and to a paged cache.
  *
- *   q, out          [batch, num_q_heads, head_dim], dtype elements, 16-byte aligned.
+ *   q, out          [batch, q_tokens, num_q_heads, head_dim], dtype elements, 16-byte aligned.
+ *   q_tokens        query tokens per sequence; 0 means 1 (a decode step). With T > 1 tokens the
+ *                   sequence's last T cached positions are the tokens' own: token t attends
+ *                   positions 0 .. seq_len - T + t (a causal limit per token), which is what T
+ *                   consecutive decode steps compute (the reference prefills token by token
+ *                   through its decode kernel, main/main_qwen3.cpp:58-65) in one pass over the
+ *                   cache. BF16 only; q_tokens * (num_q_heads / num_kv_heads) <= 16 per launch,
+ *                   more tokens run as several passes over the cache.
  *   k_cache/v_cache bases of the caches, `layout` addressing, dtype elements.
  *   seq_lens_host   [batch] cached positions attended (pos + 1) per sequence, or null.
  *   seq_lens_dev    the same on the device, or null. With a device array the kernels read
- *                   lengths from it (a captured graph stays valid as lengths grow) and the
+ *                   lengths from it (a captured graph stays valid as lengths change) and the
  *                   host copy, when also given, is used for split planning only. Without
- *                   it the host lengths must all be equal (they are passed by value).
- *   plan_len_hint   planning length when only seq_lens_dev is given (0: block capacity).
+ *                   it the host lengths must all be equal (they are passed by value). Device
+ *                   lengths are clamped to what a sequence can hold; when they outgrow what
+ *                   the workspace was planned for, the units whose partials no longer fit are
+ *                   skipped and *status_dev is set to GQA_STATUS_BAD_INPUT: plan with the
+ *                   largest lengths a replayed graph will see (plan_len_hint, or host lengths).
+ *                   Given a workspace and device lengths, the combine launch is kept whenever a
+ *                   sequence at full capacity would be split, so the launch sequence does not
+ *                   depend on the lengths.
+ *   plan_len_hint   planning length when only seq_lens_dev is given (0: block capacity). The
+ *                   workspace is then sized for full sequences, with a coarser split than the
+ *                   hint asks for if that is what fits p->workspace_bytes.
  *   block_table_dev [batch, blocks_per_seq] physical block of each logical block, or
  *                   null: every sequence then reads block `fixed_block` (the reference's
  *                   layer_id) and batch must be 1.
@@ -106,8 +132,9 @@ int gqa_layout_pool(int32_t num_blocks, int32_t block_tokens, int32_t num_kv_hea
  *                   block table; K/V rows of older positions are then requested while that
  *                   work is still finishing (the reference's decode step satisfies this: its
  *                   QKV GEMV and QK-Norm write the row of `pos` only).
- *   status_dev      optional device int32, set non-zero by a kernel whose bounded wait ran
- *                   out (it then skips its work instead of hanging).
+ *   status_dev      optional device int32, set to a GQA_STATUS_* value by a kernel whose
+ *                   bounded wait ran out (it then skips its work instead of hanging) or that
+ *                   met out-of-range device-side input.
  *   stream          cudaStream_t (null = default stream), as the reference passes it.
  */
 typedef struct gqa_decode_params {
@@ -122,7 +149,7 @@ typedef struct gqa_decode_params {
     int32_t max_ctas;
     int32_t plan_len_hint;
     int32_t early_prefetch;
-    int32_t reserved;
+    int32_t q_tokens;
     gqa_kv_layout layout;
     const void* q;
     const void* k_cache;
@@ -158,6 +185,55 @@ int gqa_decode_plan(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pla
 
 /* Launches the attention kernels on p->stream. Asynchronous. */
 int gqa_decode(const gqa_decode_params* p);
+
+/*
+ * gqa_decode() with the front stage inside the attention kernel: one launch does what
+ * kernel::fused_qk_norm_rope_kernel_cu (code/source/op/kernel/cuda/rmsnorm_kernel.cu:205-290),
+ * the KV-row placement (code/source/model/model.cpp:90-107, code/source/op/kernel/cuda/
+ * matmul_kernel.cu:238-246) and kernel::mha_kernel_cu (code/source/op/kernel/cuda/
+ * mha_kernel.cu:440-529) do in sequence. p->q holds the RAW query rows (the QKV projection's
+ * output); every CTA normalises and rotates the rows of its own unit (the same operations, hence
+ * the same bits, as gqa_qk_norm_rope_append), and the CTA that streams the chunk holding a new
+ * token's position computes that token's key row, patches it (and the value row) into its
+ * staged tile and appends both to the cache. Positions are implied: token t of sequence b sits
+ * at position seq_len_b - q_tokens + t, whose cache rows need not be written beforehand.
+ * BF16 only. With p->early_prefetch the caller promises that no work still running ahead in
+ * the stream writes these caches, the lengths or the block table at all.
+ */
+typedef struct gqa_fused_front {
+    const void* k_new;     /* [batch, q_tokens, num_kv_heads, head_dim] raw keys */
+    const void* v_new;     /* same shape, values */
+    const void* qk_weight; /* [2 * head_dim] BF16: query norm weights, then key norm weights */
+    void* q_out;           /* optional: the rotated queries, laid out like p->q; must not alias it */
+    const float* sin_cache; /* FP32 [table_len, head_dim / 2] as built by gqa_sin_cos_cache, or */
+    const float* cos_cache; /* both null: angles are computed in the kernel, same formula */
+    int32_t table_len;
+    float eps;
+} gqa_fused_front;
+
+int gqa_decode_fused(const gqa_decode_params* p, const gqa_fused_front* front);
+
+/*
+ * Attention over a SLICE of each sequence's keys that leaves, instead of the output, one record
+ * per output row [batch * q_tokens * num_q_heads][head_dim + 2] FP32 in `records`: the row's
+ * 128 channel sums relative to the slice's maximum score, that maximum (log2 domain), and the
+ * sum of the weights. p describes the slice as gqa_decode describes a whole sequence, except
+ * that a length may be 0 (a slice that holds no key of a sequence; its record is 0, -inf, 0).
+ * p->out is not written. Always needs a workspace (gqa_decode_plan's, or at least
+ * num_items * (num_q_heads / num_kv_heads) * (head_dim + 2) * 4 bytes when the plan asks for
+ * none). gqa_merge_partials turns the records of all slices into the output. No counterpart in
+ * the reference; it is the arithmetic of gqa_decode_seqpar without the exchange, for callers
+ * that move the records themselves.
+ */
+int gqa_decode_partial(const gqa_decode_params* p, float* records);
+
+/*
+ * out[row] = merge of records[part][row], part = 0 .. nparts - 1 in ascending order (the same
+ * device function gqa_decode_seqpar applies to the records of the ranks). records is
+ * [nparts][rows][head_dim + 2] FP32 on the device, out [rows][head_dim] of `dtype`.
+ */
+int gqa_merge_partials(const float* records, int32_t nparts, int64_t rows, int32_t head_dim,
+                       int32_t dtype, void* out, void* stream);
 
 /*
  * No counterpart in the reference (its caller always allocates kv_split_output,
@@ -200,6 +276,12 @@ int gqa_decode_static_scratch(const gqa_decode_params* p);
  *                   both null: angles are then computed in the kernel with the same formula.
  *   positions_host  [batch] or null; positions_dev [batch] on the device or null. One of
  *                   them is required; the device array wins.
+ *   q_tokens        new tokens per sequence; 0 means 1. Token t of sequence b sits at position
+ *                   pos_b + t; q, q_out, k_new, v_new are then [batch, q_tokens, heads, head_dim].
+ *   status_dev      optional device int32. A position read from device memory that lies
+ *                   outside the cache or the angle tables, or an unassigned block-table entry,
+ *                   skips that row and sets it to GQA_STATUS_BAD_INPUT (host positions are
+ *                   refused with GQA_ERR_RANGE before the launch).
  */
 typedef struct gqa_front_params {
     int32_t batch;
@@ -224,6 +306,9 @@ typedef struct gqa_front_params {
     const int32_t* positions_dev;
     const int32_t* block_table_dev;
     void* stream;
+    int32_t* status_dev;
+    int32_t q_tokens;
+    int32_t reserved;
 } gqa_front_params;
 
 int gqa_qk_norm_rope_append(const gqa_front_params* p);
@@ -264,11 +349,22 @@ int gqa_session_step(gqa_session* s, int32_t batch, const void* q_host, const vo
                      int32_t fixed_block, void* out_host);
 
 /*
+ * Host-side time of the last successful step in nanoseconds: [0] placing the rows in the pinned
+ * block, [1] issuing the launches, [2] waiting for the GPU, [3] handing the output over. For
+ * callers who want to see where a step's end-to-end time goes; no counterpart in the reference.
+ * A step whose kernels report a timed-out wait returns GQA_ERR_TIMEOUT, one whose kernels met an
+ * out-of-range length, position or block id returns GQA_ERR_RANGE.
+ */
+int gqa_session_last_timing(const gqa_session* s, int64_t* ns_out);
+
+/*
  * The same step on one rank of a KV-head-parallel group (see gqa_comm below): the session was
  * created with the LOCAL head counts, host rows are this rank's heads, and after the local
- * attention the outputs of all ranks are gathered on the device (ncclAllGather) before the
- * copy back. gathered_host is [nranks, batch, local_q_heads, head_dim]. Collective: every
- * rank of `comm` must call it.
+ * attention the outputs of all ranks are gathered: by the GPUs' own stores over NVLink straight
+ * into pinned host memory when gqa_comm_enable_peer_gather was called (from the combine kernel
+ * itself when units are split), else with ncclAllGather on the device and a copy.
+ * gathered_host is [nranks, batch, local_q_heads, head_dim]. Collective: every rank of `comm`
+ * must call it.
  */
 struct gqa_comm;
 int gqa_session_step_sharded(gqa_session* s, struct gqa_comm* comm, int32_t batch,
@@ -347,6 +443,12 @@ void gqa_comm_disable_peer_gather(gqa_comm* comm);
  */
 int gqa_comm_peer_gather(gqa_comm* comm, const void* send, void* recv, size_t bytes,
                          int32_t* status_dev, void* stream);
+/*
+ * 1 when an exchange of `bytes` bytes per rank would go through the peer windows, 0 when it
+ * would fall back to ncclAllGather (windows not enabled, or too small). Depends on the
+ * communicator's state and the size only, so every rank gets the same answer.
+ */
+int gqa_comm_peer_gather_fits(const gqa_comm* comm, size_t bytes);
 
 /* Rank 0 makes the id; the caller hands it to every rank (any host channel). */
 int gqa_comm_unique_id(void* id_out);
@@ -364,11 +466,15 @@ void gqa_comm_destroy(gqa_comm* comm);
  * kernel itself, row by row as rows are merged, and no separate gather kernel is launched.
  */
 int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathered);
+/* The same with the front stage inside the attention kernel (see gqa_decode_fused). */
+int gqa_decode_sharded_fused(const gqa_decode_params* p, const gqa_fused_front* front,
+                             gqa_comm* comm, void* gathered);
 
 /*
  * Sequence-parallel decode: every rank holds ALL heads but only a slice of each sequence's
  * cached keys and values (for example every N-th block, or one contiguous part). p describes
- * the LOCAL slice (local caches, local lengths, at least one key per sequence and rank). Each
+ * the LOCAL slice (local caches, local lengths; a rank that holds no key of a sequence passes
+ * length 0 for it and contributes the empty record). Each
  * rank attends over its slice; the combine kernel then sends the row's record (128 channel
  * sums relative to the slice's maximum, the maximum and the row sum) to the other ranks
  * through the peer windows and merges all ranks' records in rank order, so p->out

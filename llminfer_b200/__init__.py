@@ -5,12 +5,14 @@ the C++ shim in ``shim/`` that keeps the reference's operator interface. This Py
 is the thin binding used by the tests and the benchmark; it has no CPU fallback.
 """
 from .binding import (  # noqa: F401
+    FusedFront,
     GqaError,
     KvLayout,
     KvPool,
     Session,
     ShardComm,
     decode,
+    decode_partial,
     decode_plan,
     decode_seqpar,
     decode_sharded,
@@ -18,6 +20,7 @@ from .binding import (  # noqa: F401
     layout_pool,
     layout_reference,
     lib,
+    merge_partials,
     oproj_residual,
     oproj_workspace,
     qk_norm_rope_append,

@@ -50,7 +50,7 @@ class _DecodeParams(C.Structure):
         ("max_ctas", C.c_int32),
         ("plan_len_hint", C.c_int32),
         ("early_prefetch", C.c_int32),
-        ("reserved", C.c_int32),
+        ("q_tokens", C.c_int32),
         ("layout", _Layout),
         ("q", C.c_void_p),
         ("k_cache", C.c_void_p),
@@ -102,6 +102,22 @@ class _FrontParams(C.Structure):
         ("positions_dev", C.c_void_p),
         ("block_table_dev", C.c_void_p),
         ("stream", C.c_void_p),
+        ("status_dev", C.c_void_p),
+        ("q_tokens", C.c_int32),
+        ("reserved", C.c_int32),
+    ]
+
+
+class _FusedFront(C.Structure):
+    _fields_ = [
+        ("k_new", C.c_void_p),
+        ("v_new", C.c_void_p),
+        ("qk_weight", C.c_void_p),
+        ("q_out", C.c_void_p),
+        ("sin_cache", C.c_void_p),
+        ("cos_cache", C.c_void_p),
+        ("table_len", C.c_int32),
+        ("eps", C.c_float),
     ]
 
 
@@ -154,6 +170,10 @@ _SIGNATURES = {
     "gqa_decode_plan": (C.c_int, [C.POINTER(_DecodeParams), C.c_int32, C.POINTER(_PlanInfo)]),
     "gqa_decode": (C.c_int, [C.POINTER(_DecodeParams)]),
     "gqa_decode_static_scratch": (C.c_int, [C.POINTER(_DecodeParams)]),
+    "gqa_decode_fused": (C.c_int, [C.POINTER(_DecodeParams), C.POINTER(_FusedFront)]),
+    "gqa_decode_partial": (C.c_int, [C.POINTER(_DecodeParams), C.c_void_p]),
+    "gqa_merge_partials": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int32,
+                                     C.c_void_p, C.c_void_p]),
     "gqa_qk_norm_rope_append": (C.c_int, [C.POINTER(_FrontParams)]),
     "gqa_sin_cos_cache": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "gqa_session_create": (C.c_int, [C.c_int32] * 6 + [C.POINTER(C.c_void_p)]),
@@ -166,6 +186,8 @@ _SIGNATURES = {
                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                            C.c_void_p, C.POINTER(_Layout), C.POINTER(C.c_int32),
                                            C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "gqa_session_last_timing": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64)]),
+    "gqa_comm_peer_gather_fits": (C.c_int, [C.c_void_p, C.c_size_t]),
     "gqa_kv_pool_bytes": (C.c_size_t, [C.c_int32] * 5),
     "gqa_kv_pool_create": (C.c_int, [C.c_int32] * 7 + [C.POINTER(C.c_void_p)]),
     "gqa_kv_pool_destroy": (None, [C.c_void_p]),
@@ -186,6 +208,8 @@ _SIGNATURES = {
     "gqa_comm_init": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
     "gqa_comm_destroy": (None, [C.c_void_p]),
     "gqa_decode_sharded": (C.c_int, [C.POINTER(_DecodeParams), C.c_void_p, C.c_void_p]),
+    "gqa_decode_sharded_fused": (C.c_int, [C.POINTER(_DecodeParams), C.POINTER(_FusedFront),
+                                           C.c_void_p, C.c_void_p]),
     "gqa_decode_seqpar": (C.c_int, [C.POINTER(_DecodeParams), C.c_void_p]),
     "gqa_oproj_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "gqa_qkv_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
@@ -282,10 +306,14 @@ def _int_array(values: Optional[Sequence[int]]):
 def _decode_params(q, k_cache, v_cache, out, layout, seq_lens_host, seq_lens_dev, block_table,
                    fixed_block, workspace, split_keys, max_ctas, plan_len_hint, status, stream,
                    keep, early_prefetch=False):
-    batch, hq, d = q.shape
+    if q.dim() == 4:  # [batch, q_tokens, heads, head_dim]
+        batch, tokens, hq, d = q.shape
+    else:
+        (batch, hq, d), tokens = q.shape, 1
     p = _DecodeParams()
     p.dtype = _dtype_code(q)
     p.batch, p.num_q_heads, p.head_dim = batch, hq, d
+    p.q_tokens = tokens
     p.num_kv_heads = keep["num_kv_heads"]
     p.blocks_per_seq = 0 if block_table is None else block_table.shape[1]
     p.fixed_block = fixed_block
@@ -311,13 +339,14 @@ def decode_plan(*, dtype: int, batch: int, num_q_heads: int, num_kv_heads: int, 
                 seq_lens: Optional[Sequence[int]], blocks_per_seq: int = 0, fixed_block: int = 0,
                 split_keys: int = 0, max_ctas: int = 0, plan_len_hint: int = 0,
                 workspace_bytes: int = 0, sm_count: int = 148, paged: bool = False,
-                device_lens: bool = False, head_dim: int = 128) -> dict:
+                device_lens: bool = False, head_dim: int = 128, q_tokens: int = 0) -> dict:
     """Host-only split planning (no device memory is touched; pointers are placeholders)."""
     p = _DecodeParams()
     p.dtype, p.batch, p.num_q_heads, p.num_kv_heads, p.head_dim = (
         dtype, batch, num_q_heads, num_kv_heads, head_dim)
     p.blocks_per_seq, p.fixed_block = blocks_per_seq, fixed_block
     p.split_keys, p.max_ctas, p.plan_len_hint = split_keys, max_ctas, plan_len_hint
+    p.q_tokens = q_tokens
     p.layout = layout.c()
     fake = 0x1000  # validation only looks at nullness and alignment
     p.q = p.k_cache = p.v_cache = p.out = fake
@@ -338,15 +367,68 @@ def decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: t
            block_table: Optional[torch.Tensor] = None, fixed_block: int = 0,
            workspace: Optional[torch.Tensor] = None, split_keys: int = 0, max_ctas: int = 0,
            plan_len_hint: int = 0, status: Optional[torch.Tensor] = None,
-           stream: Optional[int] = None, early_prefetch: bool = False) -> None:
-    """Decode attention for q [batch, num_q_heads, 128] on the current stream (or `stream`)."""
+           stream: Optional[int] = None, early_prefetch: bool = False,
+           front: Optional["FusedFront"] = None) -> None:
+    """Decode attention for q [batch, num_q_heads, 128] (or [batch, q_tokens, num_q_heads, 128])
+    on the current stream (or `stream`). With `front`, q holds the raw query rows and the
+    kernel runs QK-Norm + RoPE + KV append itself (gqa_decode_fused)."""
     if stream is None:
         stream = torch.cuda.current_stream().cuda_stream
     keep = {"num_kv_heads": num_kv_heads}
     p = _decode_params(q, k_cache, v_cache, out, layout, seq_lens, seq_lens_dev, block_table,
                        fixed_block, workspace, split_keys, max_ctas, plan_len_hint, status,
                        stream, keep, early_prefetch)
-    _check(lib().gqa_decode(C.byref(p)), "gqa_decode")
+    if front is None:
+        _check(lib().gqa_decode(C.byref(p)), "gqa_decode")
+    else:
+        f = front.c()
+        _check(lib().gqa_decode_fused(C.byref(p), C.byref(f)), "gqa_decode_fused")
+
+
+@dataclass
+class FusedFront:
+    """Inputs of the front stage when it runs inside the attention kernel (gqa_fused_front)."""
+    k_new: torch.Tensor
+    v_new: torch.Tensor
+    qk_weight: torch.Tensor
+    q_out: Optional[torch.Tensor] = None
+    sin_cache: Optional[torch.Tensor] = None
+    cos_cache: Optional[torch.Tensor] = None
+    eps: float = 1e-6
+
+    def c(self) -> _FusedFront:
+        f = _FusedFront()
+        f.k_new, f.v_new, f.qk_weight = _ptr(self.k_new), _ptr(self.v_new), _ptr(self.qk_weight)
+        f.q_out = _ptr(self.q_out)
+        f.sin_cache, f.cos_cache = _ptr(self.sin_cache), _ptr(self.cos_cache)
+        f.table_len = 0 if self.sin_cache is None else self.sin_cache.shape[0]
+        f.eps = self.eps
+        return f
+
+
+def decode_partial(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                   records: torch.Tensor, *, num_kv_heads: int, layout: KvLayout,
+                   seq_lens: Optional[Sequence[int]] = None,
+                   seq_lens_dev: Optional[torch.Tensor] = None,
+                   block_table: Optional[torch.Tensor] = None, fixed_block: int = 0,
+                   workspace: Optional[torch.Tensor] = None, split_keys: int = 0,
+                   status: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """Attention over a slice of the keys; leaves records [batch * heads, 130] FP32."""
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    keep = {"num_kv_heads": num_kv_heads}
+    p = _decode_params(q, k_cache, v_cache, q, layout, seq_lens, seq_lens_dev, block_table,
+                       fixed_block, workspace, split_keys, 0, 0, status, stream, keep)
+    _check(lib().gqa_decode_partial(C.byref(p), _ptr(records)), "gqa_decode_partial")
+
+
+def merge_partials(records: torch.Tensor, out: torch.Tensor, stream: Optional[int] = None) -> None:
+    """records [nparts, rows, 130] FP32 -> out [rows..., 128] (BF16 or FP32)."""
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    nparts, rows, _ = records.shape
+    _check(lib().gqa_merge_partials(_ptr(records), nparts, rows, out.shape[-1], _dtype_code(out),
+                                    _ptr(out), stream), "gqa_merge_partials")
 
 
 STATIC_SCRATCH_BYTES = 8 << 20
@@ -388,12 +470,20 @@ def qk_norm_rope_append(q: torch.Tensor, k_new: torch.Tensor, v_new: Optional[to
                         sin_cache: Optional[torch.Tensor] = None,
                         cos_cache: Optional[torch.Tensor] = None,
                         block_table: Optional[torch.Tensor] = None, fixed_block: int = 0,
-                        eps: float = 1e-6, stream: Optional[int] = None) -> None:
+                        eps: float = 1e-6, stream: Optional[int] = None,
+                        status: Optional[torch.Tensor] = None) -> None:
+    """q is [batch, heads, 128] or, for several new tokens per sequence, [batch, tokens, heads,
+    128] (k_new and v_new likewise); positions are those of each sequence's first new token."""
     if stream is None:
         stream = torch.cuda.current_stream().cuda_stream
-    batch, hq, d = q.shape
+    if q.dim() == 4:
+        batch, tokens, hq, d = q.shape
+    else:
+        (batch, hq, d), tokens = q.shape, 1
     f = _FrontParams()
-    f.batch, f.num_q_heads, f.num_kv_heads, f.head_dim = batch, hq, k_new.shape[1], d
+    f.batch, f.num_q_heads, f.num_kv_heads, f.head_dim = batch, hq, k_new.shape[-2], d
+    f.q_tokens = tokens
+    f.status_dev = _ptr(status)
     f.blocks_per_seq = 0 if block_table is None else block_table.shape[1]
     f.fixed_block = fixed_block
     f.table_len = 0 if sin_cache is None else sin_cache.shape[0]
@@ -449,6 +539,12 @@ class Session:
                 self._h, comm._h, q_host.shape[0], _ptr(q_host), _ptr(k_host), _ptr(v_host),
                 _ptr(qk_weight), _ptr(k_cache), _ptr(v_cache), C.byref(lay), pos,
                 _ptr(block_table), bps, fixed_block, _ptr(out_host)), "gqa_session_step_sharded")
+
+    def last_timing(self) -> dict:
+        """Host-side nanoseconds of the last step: staging, launches, wait, copy-out."""
+        ns = (C.c_int64 * 4)()
+        _check(lib().gqa_session_last_timing(self._h, ns), "gqa_session_last_timing")
+        return dict(zip(("stage_ns", "launch_ns", "wait_ns", "copy_out_ns"), ns))
 
     def close(self) -> None:
         if self._h:
@@ -575,7 +671,13 @@ def decode_sharded(comm: ShardComm, gathered: torch.Tensor, q, k_cache, v_cache,
                        kw.get("workspace"), kw.get("split_keys", 0), kw.get("max_ctas", 0),
                        kw.get("plan_len_hint", 0), kw.get("status"), stream, keep,
                        kw.get("early_prefetch", False))
-    _check(lib().gqa_decode_sharded(C.byref(p), comm._h, _ptr(gathered)), "gqa_decode_sharded")
+    front = kw.get("front")
+    if front is None:
+        _check(lib().gqa_decode_sharded(C.byref(p), comm._h, _ptr(gathered)), "gqa_decode_sharded")
+    else:
+        f = front.c()
+        _check(lib().gqa_decode_sharded_fused(C.byref(p), C.byref(f), comm._h, _ptr(gathered)),
+               "gqa_decode_sharded_fused")
 
 
 def decode_seqpar(comm: ShardComm, q, k_cache, v_cache, out, *, num_kv_heads: int,

@@ -31,7 +31,7 @@ KERNEL_SOURCES = [
     "csrc/proj.cu",
 ]
 KERNEL_HEADERS = ["csrc/ptx.cuh", "csrc/work_map.cuh", "csrc/decode_kernels.cuh",
-                  "csrc/peer_window.cuh"]
+                  "csrc/peer_window.cuh", "csrc/front_math.cuh"]
 
 
 def _stale(output: Path, inputs: list[Path]) -> bool:

@@ -14,17 +14,34 @@
 // CTA keeps WARPS * STAGES * 16 KiB in flight, with no CTA-wide synchronisation inside an
 // item.
 //
-// Math. Scores are computed transposed, S^T[key][head] = K[key][:] . Q[head][:], on tensor
-// cores (mma.sync m16n8k16, BF16 in, FP32 out) with the 16 keys on M and the (up to 8) query
-// heads of the group on N, so the group costs one MMA column block whatever its width.
-// Online softmax runs in FP32 in the exp2 domain; probabilities are rounded to BF16 (the
-// row sum uses the rounded values, so the weights still sum to one), transposed with
-// movmatrix and used as the B operand of O^T[channel][head] += V^T[channel][key] . P^T.
+// Math. Scores are computed transposed, S^T[key][column] = K[key][:] . Q[column][:], on tensor
+// cores (mma.sync m16n8k16, BF16 in, FP32 out) with the 16 keys on M and the columns of the
+// unit on N. A column is a (query token, query head) pair: a decode step has one token and
+// the (up to 8) heads of the group fill one N tile; with several query tokens per sequence
+// (the reference prefills token by token through its decode kernel, main/main_qwen3.cpp:58-65)
+// the tokens sit side by side on N, NT tiles of 8 columns, and column (t, n) sees keys
+// 0 .. len - q_tokens + t only (a causal limit per column). Online softmax runs in FP32 in
+// the exp2 domain; probabilities are rounded to BF16 (the row sum uses the rounded values, so
+// the weights still sum to one), transposed with movmatrix and used as the B operand of
+// O^T[channel][column] += V^T[channel][key] . P^T.
 //
 // Each warp keeps (m, l, O) for the chunks it consumed; at the end of an item the warps are
 // merged through shared memory in warp order and the CTA writes either the final BF16
 // output (unit not split) or an FP32 partial record for the combine kernel.
+//
+// FUSED adds the stage the reference runs in front of attention
+// (fused_qk_norm_rope_kernel, code/source/op/kernel/cuda/rmsnorm_kernel.cu:205-290, and the
+// KV-row placement of code/source/model/model.cpp:90-107) to the same launch: every CTA
+// normalises and rotates the raw query rows of its unit itself (front_math.cuh: the same
+// operations, hence the same bits, as the stand-alone front kernel), and the warp that
+// consumes the stage holding a new token's position computes that token's key row, copies its
+// value row, patches both into the staged tile in shared memory and appends them to the cache
+// in HBM. Nothing else in the launch reads those cache rows, so no ordering between CTAs is
+// needed.
+#include <mutex>
+
 #include "decode_kernels.cuh"
+#include "front_math.cuh"
 #include "ptx.cuh"
 #include "work_map.cuh"
 
@@ -32,8 +49,8 @@ namespace gqa {
 
 namespace {
 
-constexpr int kOPitch = 132;                        // floats per head in the merge buffer
-constexpr int kHeadsPad = 8;                        // MMA N
+constexpr int kOPitch = 132;                        // floats per column in the merge buffer
+constexpr int kQPitch = 136;                        // BF16 per column of the rotated-query buffer
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;   // bounded wait for a staged chunk
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
@@ -61,7 +78,7 @@ struct Cursor {
     int32_t item;
     int32_t k;
     int32_t k_end;
-    int32_t k_last;  // stage holding the newest position of the sequence
+    int32_t k_new;  // first stage that holds a position of the new tokens
     int32_t b;
     int32_t hk;
     bool valid;
@@ -69,28 +86,30 @@ struct Cursor {
 
 }  // namespace
 
-template <int WARPS, int STAGES, int KEYS, int OCC>
+template <int WARPS, int STAGES, int KEYS, int OCC, int NT, bool FUSED>
 __global__ void __launch_bounds__(WARPS * 32, OCC)
 gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
-                       const __grid_constant__ CUtensorMap tmap_v, const DecodeArgs a) {
+                       const __grid_constant__ CUtensorMap tmap_v, const DecodeArgs a,
+                       const FusedFrontArgs ff) {
     constexpr int kHalfBytes = KEYS * 128;       // one 64-channel half of K or V of a stage
     constexpr int kTileBytes = 2 * kHalfBytes;   // K or V of a stage
     constexpr int kStageBytes = 2 * kTileBytes;  // K + V
     constexpr int MT = KEYS / 16;                // 16-key MMA tiles per stage
+    constexpr int kCols = 8 * NT;                // columns of the MMA N side
     extern __shared__ uint8_t smem_raw[];
     // The swizzle pattern is a function of the shared-memory address: stages sit on 1 KiB.
     uint8_t* smem = reinterpret_cast<uint8_t*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* ring_all = smem;
     float* s_o = reinterpret_cast<float*>(ring_all + WARPS * STAGES * kStageBytes);
-    float* s_m = s_o + WARPS * kHeadsPad * kOPitch;
-    float* s_l = s_m + WARPS * kHeadsPad;
-    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_l + WARPS * kHeadsPad);
-    int32_t* s_tables = reinterpret_cast<int32_t*>(s_bar + WARPS * STAGES);
+    float* s_m = s_o + WARPS * kCols * kOPitch;
+    float* s_l = s_m + WARPS * kCols;
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_l + WARPS * kCols);
+    __nv_bfloat16* s_q = reinterpret_cast<__nv_bfloat16*>(s_bar + WARPS * STAGES);
+    int32_t* s_tables = reinterpret_cast<int32_t*>(s_q + (FUSED ? kCols * kQPitch : 0));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    timeline_mark(0, a.fixed_block);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < WARPS * STAGES; ++i) mbar_init(smem_u32(&s_bar[i]), 1);
@@ -103,16 +122,18 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     pdl_launch_dependents();
     // Everything up to pdl_wait() overlaps the previous kernel of the stream. With
     // a.early_prefetch the caller has promised that nothing still running ahead of this
-    // kernel writes cache rows other than the newest position of each sequence, nor the
-    // lengths or the block table: stages that do not hold a newest position are then
+    // kernel writes cache rows other than the new positions of each sequence, nor the
+    // lengths or the block table: stages that do not hold a new position are then
     // requested before the wait, which hides the DRAM ramp behind the predecessor's tail.
+    // (FUSED: this kernel writes the new rows itself, so every stage may be requested.)
     if (!a.early_prefetch) pdl_wait();
-    timeline_mark(1, a.fixed_block);
     const WorkTables tables = build_work_tables(a, s_tables);
     __syncthreads();
 
     const int32_t n_items = total_items(a, tables);
     const int32_t group = a.group;
+    const int32_t q_tokens = a.q_tokens;
+    const int32_t cols = group * q_tokens;
     const uint64_t policy = l2_policy_evict_first();
     const uint32_t ring = smem_u32(ring_all + warp * STAGES * kStageBytes);
     const uint32_t bars = smem_u32(&s_bar[warp * STAGES]);
@@ -122,7 +143,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     prod.item = blockIdx.x - gridDim.x;
     prod.k = 0;
     prod.k_end = 0;
-    prod.k_last = 0;
+    prod.k_new = 0;
     prod.b = 0;
     prod.hk = 0;
     prod.valid = true;
@@ -137,7 +158,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                 c.hk = it.hk;
                 c.k = it.chunk_begin * kChunkKeys / KEYS + warp;
                 c.k_end = ceil_div(min(it.len, it.chunk_end * kChunkKeys), KEYS);
-                c.k_last = (it.len - 1) / KEYS;
+                c.k_new = (it.len - q_tokens) / KEYS;
             }
         }
     };
@@ -155,6 +176,9 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
             blk = __ldg(a.block_table + (int64_t)prod.b * a.blocks_per_seq + lb);
         }
         if (lane == 0) {
+            // A block id outside the cache reads as zeros (the copy engine fills what lies
+            // outside the tensor) and is reported.
+            if ((uint32_t)blk >= (uint32_t)a.num_blocks) raise_status(a, kStatusBadInput);
             const uint32_t bar = bars + stage * 8;
             const uint32_t dst = ring + stage * kStageBytes;
             fence_proxy_async();
@@ -175,7 +199,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     if (a.early_prefetch) {
 #pragma unroll 1
         for (int s = 0; s < STAGES; ++s) {
-            if (!prod.valid || prod.k == prod.k_last) break;
+            if (!prod.valid || (!FUSED && prod.k >= prod.k_new)) break;
             issue();
         }
         pdl_wait();
@@ -198,35 +222,91 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
 #pragma unroll 1
     for (int32_t item = blockIdx.x; item < n_items; item += gridDim.x) {
         const Item it = decode_item(a, tables, item);
+        const int32_t new_lo = it.len - q_tokens;  // position of the first query token
 
-        // Query group as B fragments: B[k = channel][n = head] = Q[head][channel].
-        uint32_t qf[8][2];
-        {
-            const int n = lane >> 2;
-            const __nv_bfloat16* qrow = reinterpret_cast<const __nv_bfloat16*>(a.q) +
-                ((int64_t)it.b * a.num_q_heads + (int64_t)it.hk * group + n) * kHeadDim +
-                2 * (lane & 3);
+        // Row of column c in q / out: [sequence][token][query head][channel].
+        auto q_row_of = [&](int c) -> int64_t {
+            const int t = c / group;
+            const int n = c - t * group;
+            return (((int64_t)it.b * a.q_token_stride + a.q_token_first + t) * a.num_q_heads +
+                    (int64_t)it.hk * group + n) * kHeadDim;
+        };
+
+        if (FUSED) {
+            // QK-Norm + RoPE of this unit's raw query rows, one warp per column.
+            const __nv_bfloat16* wei = reinterpret_cast<const __nv_bfloat16*>(ff.qk_weight);
+            for (int c = warp; c < cols; c += WARPS) {
+                const int32_t pos = new_lo + c / group;
+                const bool tab = ff.sin_cache != nullptr && pos < ff.table_len;
+                const float* sin_row = tab ? ff.sin_cache + (int64_t)pos * (kHeadDim / 2) : nullptr;
+                const float* cos_row = tab ? ff.cos_cache + (int64_t)pos * (kHeadDim / 2) : nullptr;
+                const int64_t row = q_row_of(c);
+                __nv_bfloat16 y[4];
+                front_norm_rope(reinterpret_cast<const __nv_bfloat16*>(a.q) + row, wei, sin_row,
+                                cos_row, pos, ff.eps, lane, y);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) s_q[c * kQPitch + lane + 32 * i] = y[i];
+                if (it.split == 0 && ff.q_out != nullptr) {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ff.q_out) + row;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) dst[lane + 32 * i] = y[i];
+                }
+            }
+            __syncthreads();
+        }
+
+        // Query columns as B fragments: B[k = channel][n = column] = Q[column][channel].
+        uint32_t qf[NT][8][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int c = nt * 8 + (lane >> 2);
+            const __nv_bfloat16* qrow =
+                FUSED ? s_q + c * kQPitch + 2 * (lane & 3)
+                      : reinterpret_cast<const __nv_bfloat16*>(a.q) + q_row_of(c < cols ? c : 0) +
+                            2 * (lane & 3);
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
-                if (n < group) {
-                    qf[ks][0] = __ldcg(reinterpret_cast<const uint32_t*>(qrow + ks * 16));
-                    qf[ks][1] = __ldcg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8));
+                if (c < cols) {
+                    if (FUSED) {
+                        qf[nt][ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16);
+                        qf[nt][ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8);
+                    } else {
+                        qf[nt][ks][0] = __ldcg(reinterpret_cast<const uint32_t*>(qrow + ks * 16));
+                        qf[nt][ks][1] = __ldcg(reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8));
+                    }
                 } else {
-                    qf[ks][0] = 0u;
-                    qf[ks][1] = 0u;
+                    qf[nt][ks][0] = 0u;
+                    qf[nt][ks][1] = 0u;
                 }
             }
         }
 
-        float m0 = -INFINITY, m1 = -INFINITY;  // running maxima of heads 2*(lane&3), +1
-        float l0 = 0.0f, l1 = 0.0f;            // this lane's share of the running sums
-        float o[8][4];
+        const int32_t key_end = min(it.len, it.chunk_end * kChunkKeys);
+        // Causal limit of this lane's columns (2 per N tile): keys [0, lim) are visible.
+        int32_t lim[NT][2];
 #pragma unroll
-        for (int dt = 0; dt < 8; ++dt) {
-            o[dt][0] = 0.0f; o[dt][1] = 0.0f; o[dt][2] = 0.0f; o[dt][3] = 0.0f;
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int c = nt * 8 + 2 * (lane & 3) + e;
+                const int t = c < cols ? c / group : q_tokens - 1;
+                lim[nt][e] = min(key_end, new_lo + t + 1);
+            }
+        }
+        const int32_t lim_min = min(key_end, new_lo + 1);
+
+        float m[NT][2], l[NT][2];  // running maxima and this lane's share of the running sums
+        float o[NT][8][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            m[nt][0] = -INFINITY; m[nt][1] = -INFINITY;
+            l[nt][0] = 0.0f; l[nt][1] = 0.0f;
+#pragma unroll
+            for (int dt = 0; dt < 8; ++dt) {
+                o[nt][dt][0] = 0.0f; o[nt][dt][1] = 0.0f; o[nt][dt][2] = 0.0f; o[nt][dt][3] = 0.0f;
+            }
         }
 
-        const int32_t key_end = min(it.len, it.chunk_end * kChunkKeys);
         const int32_t k_end = ceil_div(key_end, KEYS);
 #pragma unroll 1
         for (int32_t k = it.chunk_begin * kChunkKeys / KEYS + warp; k < k_end; k += WARPS) {
@@ -235,17 +315,67 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
             const uint32_t parity = (consumed / STAGES) & 1u;
             if (!wait_stage(bars + stage * 8, parity)) {
                 dead = true;
-                if (lane == 0 && a.status != nullptr) atomicExch(a.status, 1);
+                if (lane == 0) raise_status(a, kStatusStageTimeout);
                 break;
-            }
-            if (consumed == 0) {
-                timeline_mark(2, a.fixed_block);
-                timeline_cta(0);
-                timeline_cta(1);
             }
             const uint32_t kbase = ring + stage * kStageBytes;
             const uint32_t vbase = kbase + kTileBytes;
             const int32_t valid = key_end - k * KEYS;  // keys of this stage inside the item
+
+            if (FUSED && (k + 1) * KEYS > new_lo) {
+                // The stage holds positions of the new tokens, whose rows are not in the cache
+                // yet: compute them, patch the staged tile and append them to the cache.
+                uint8_t* kptr = ring_all + (warp * STAGES + stage) * kStageBytes;
+                const __nv_bfloat16* wei =
+                    reinterpret_cast<const __nv_bfloat16*>(ff.qk_weight) + kHeadDim;
+#pragma unroll 1
+                for (int t = 0; t < q_tokens; ++t) {
+                    const int32_t pos = new_lo + t;
+                    const int32_t r = pos - k * KEYS;
+                    if (r < 0 || r >= KEYS) continue;
+                    int32_t blk = a.fixed_block;
+                    int32_t tok = pos;
+                    if (a.block_table != nullptr) {
+                        const int32_t lb = pos / a.block_tokens;
+                        tok = pos - lb * a.block_tokens;
+                        blk = __ldg(a.block_table + (int64_t)it.b * a.blocks_per_seq + lb);
+                    }
+                    const bool blk_ok = (uint32_t)blk < (uint32_t)a.num_blocks;
+                    const int64_t cache_off = (int64_t)blk * a.stride_block +
+                                              (int64_t)tok * a.stride_token +
+                                              (int64_t)it.hk * a.stride_head;
+                    const int64_t new_off =
+                        (((int64_t)it.b * a.q_token_stride + a.q_token_first + t) * a.num_kv_heads +
+                         it.hk) * kHeadDim;
+                    const bool tab = ff.sin_cache != nullptr && pos < ff.table_len;
+                    const float* sin_row = tab ? ff.sin_cache + (int64_t)pos * (kHeadDim / 2) : nullptr;
+                    const float* cos_row = tab ? ff.cos_cache + (int64_t)pos * (kHeadDim / 2) : nullptr;
+                    __nv_bfloat16 y[4];
+                    front_norm_rope(reinterpret_cast<const __nv_bfloat16*>(ff.k_new) + new_off, wei,
+                                    sin_row, cos_row, pos, ff.eps, lane, y);
+                    __nv_bfloat16* k_dst = reinterpret_cast<__nv_bfloat16*>(
+                                               const_cast<void*>(a.k_cache)) + cache_off;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int c64 = lane + 32 * (i & 1);
+                        *reinterpret_cast<__nv_bfloat16*>(
+                            kptr + (i >> 1) * kHalfBytes + r * 128 +
+                            ((((c64 >> 3) ^ (r & 7))) << 4) + (c64 & 7) * 2) = y[i];
+                        if (blk_ok) k_dst[lane + 32 * i] = y[i];
+                    }
+                    const uint2 vv = __ldcg(reinterpret_cast<const uint2*>(
+                                                reinterpret_cast<const __nv_bfloat16*>(ff.v_new) +
+                                                new_off) + lane);
+                    *reinterpret_cast<uint2*>(kptr + kTileBytes + (lane >> 4) * kHalfBytes + r * 128 +
+                                              (((((lane & 15) >> 1) ^ (r & 7))) << 4) +
+                                              (lane & 1) * 8) = vv;
+                    if (blk_ok) {
+                        reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(
+                            const_cast<void*>(a.v_cache)) + cache_off)[lane] = vv;
+                    }
+                }
+                __syncwarp();
+            }
 
             if (valid < KEYS) {
                 // Rows past the sequence end hold whatever the cache holds there. Zero those
@@ -264,10 +394,13 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
             }
 
             // ---- S^T = K . Q^T for MT tiles of 16 keys ----------------------------------
-            float s[MT][4];
+            float s[NT][MT][4];
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                s[mt][0] = 0.0f; s[mt][1] = 0.0f; s[mt][2] = 0.0f; s[mt][3] = 0.0f;
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    s[nt][mt][0] = 0.0f; s[nt][mt][1] = 0.0f; s[nt][mt][2] = 0.0f; s[nt][mt][3] = 0.0f;
+                }
             }
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
@@ -277,61 +410,82 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                     uint32_t a0, a1, a2, a3;
                     ldmatrix_x4(kbase + (ks >> 2) * kHalfBytes + mt * 2048 + k_row_off + col,
                                 a0, a1, a2, a3);
-                    mma_bf16_16816(s[mt], a0, a1, a2, a3, qf[ks][0], qf[ks][1]);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        mma_bf16_16816(s[nt][mt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+                    }
                 }
             }
 
             // ---- online softmax (exp2 domain) -------------------------------------------
+            uint32_t pb[NT][MT][2];
+            bool rescale = false;
+            float alpha[NT][2];
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) s[mt][c] *= a.scale_log2;
-            }
-            if (valid < KEYS) {
+            for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    const int key = mt * 16 + (lane >> 2);
-                    if (key >= valid) { s[mt][0] = -INFINITY; s[mt][1] = -INFINITY; }
-                    if (key + 8 >= valid) { s[mt][2] = -INFINITY; s[mt][3] = -INFINITY; }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) s[nt][mt][c] *= a.scale_log2;
                 }
-            }
-            float c0 = fmaxf(s[0][0], s[0][2]);
-            float c1 = fmaxf(s[0][1], s[0][3]);
+                if ((k + 1) * KEYS > lim_min) {
+                    // Keys past the item's end and keys a column's token may not see yet.
+                    const int32_t v0 = lim[nt][0] - k * KEYS;
+                    const int32_t v1 = lim[nt][1] - k * KEYS;
 #pragma unroll
-            for (int mt = 1; mt < MT; ++mt) {
-                c0 = fmaxf(c0, fmaxf(s[mt][0], s[mt][2]));
-                c1 = fmaxf(c1, fmaxf(s[mt][1], s[mt][3]));
-            }
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const int key = mt * 16 + (lane >> 2);
+                        if (key >= v0) s[nt][mt][0] = -INFINITY;
+                        if (key >= v1) s[nt][mt][1] = -INFINITY;
+                        if (key + 8 >= v0) s[nt][mt][2] = -INFINITY;
+                        if (key + 8 >= v1) s[nt][mt][3] = -INFINITY;
+                    }
+                }
+                float c0 = fmaxf(s[nt][0][0], s[nt][0][2]);
+                float c1 = fmaxf(s[nt][0][1], s[nt][0][3]);
 #pragma unroll
-            for (int d = 4; d < 32; d <<= 1) {
-                c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, d));
-                c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, d));
-            }
-            const float n0 = fmaxf(m0, c0);
-            const float n1 = fmaxf(m1, c1);
-            const float alpha0 = ex2_approx(m0 - n0);
-            const float alpha1 = ex2_approx(m1 - n1);
-            m0 = n0;
-            m1 = n1;
+                for (int mt = 1; mt < MT; ++mt) {
+                    c0 = fmaxf(c0, fmaxf(s[nt][mt][0], s[nt][mt][2]));
+                    c1 = fmaxf(c1, fmaxf(s[nt][mt][1], s[nt][mt][3]));
+                }
+#pragma unroll
+                for (int d = 4; d < 32; d <<= 1) {
+                    c0 = fmaxf(c0, __shfl_xor_sync(0xffffffffu, c0, d));
+                    c1 = fmaxf(c1, __shfl_xor_sync(0xffffffffu, c1, d));
+                }
+                const float n0 = fmaxf(m[nt][0], c0);
+                const float n1 = fmaxf(m[nt][1], c1);
+                const float e0 = safe_max(n0);
+                const float e1 = safe_max(n1);
+                alpha[nt][0] = ex2_approx(m[nt][0] - e0);
+                alpha[nt][1] = ex2_approx(m[nt][1] - e1);
+                m[nt][0] = n0;
+                m[nt][1] = n1;
 
-            uint32_t pb[MT][2];
-            float add0 = 0.0f, add1 = 0.0f;
+                float add0 = 0.0f, add1 = 0.0f;
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const uint32_t p01 = pack_bf16(ex2_approx(s[mt][0] - n0), ex2_approx(s[mt][1] - n1));
-                const uint32_t p23 = pack_bf16(ex2_approx(s[mt][2] - n0), ex2_approx(s[mt][3] - n1));
-                add0 += bf16_lo_to_f32(p01) + bf16_lo_to_f32(p23);
-                add1 += bf16_hi_to_f32(p01) + bf16_hi_to_f32(p23);
-                pb[mt][0] = movmatrix_trans(p01);
-                pb[mt][1] = movmatrix_trans(p23);
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint32_t p01 = pack_bf16(ex2_approx(s[nt][mt][0] - e0),
+                                                   ex2_approx(s[nt][mt][1] - e1));
+                    const uint32_t p23 = pack_bf16(ex2_approx(s[nt][mt][2] - e0),
+                                                   ex2_approx(s[nt][mt][3] - e1));
+                    add0 += bf16_lo_to_f32(p01) + bf16_lo_to_f32(p23);
+                    add1 += bf16_hi_to_f32(p01) + bf16_hi_to_f32(p23);
+                    pb[nt][mt][0] = movmatrix_trans(p01);
+                    pb[nt][mt][1] = movmatrix_trans(p23);
+                }
+                l[nt][0] = l[nt][0] * alpha[nt][0] + add0;
+                l[nt][1] = l[nt][1] * alpha[nt][1] + add1;
+                rescale = rescale || (alpha[nt][0] != 1.0f) || (alpha[nt][1] != 1.0f);
             }
-            l0 = l0 * alpha0 + add0;
-            l1 = l1 * alpha1 + add1;
-            if (__any_sync(0xffffffffu, (alpha0 != 1.0f) || (alpha1 != 1.0f))) {
+            if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-                for (int dt = 0; dt < 8; ++dt) {
-                    o[dt][0] *= alpha0; o[dt][1] *= alpha1;
-                    o[dt][2] *= alpha0; o[dt][3] *= alpha1;
+                for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                    for (int dt = 0; dt < 8; ++dt) {
+                        o[nt][dt][0] *= alpha[nt][0]; o[nt][dt][1] *= alpha[nt][1];
+                        o[nt][dt][2] *= alpha[nt][0]; o[nt][dt][3] *= alpha[nt][1];
+                    }
                 }
             }
 
@@ -344,7 +498,10 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                     uint32_t a0, a1, a2, a3;
                     ldmatrix_x4_trans(vbase + (dt >> 2) * kHalfBytes + kt * 2048 + v_row_off + col,
                                       a0, a1, a2, a3);
-                    mma_bf16_16816(o[dt], a0, a1, a2, a3, pb[kt][0], pb[kt][1]);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        mma_bf16_16816(o[nt][dt], a0, a1, a2, a3, pb[nt][kt][0], pb[nt][kt][1]);
+                    }
                 }
             }
 
@@ -354,127 +511,120 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
         }
 
         // ---- merge the warps of this CTA ---------------------------------------------------
-        timeline_mark(3, a.fixed_block);
-        timeline_cta(2);
 #pragma unroll
-        for (int d = 4; d < 32; d <<= 1) {
-            l0 += __shfl_xor_sync(0xffffffffu, l0, d);
-            l1 += __shfl_xor_sync(0xffffffffu, l1, d);
-        }
-        {
-            const int h0 = 2 * (lane & 3);
-            if (lane < 4) {
-                s_m[warp * kHeadsPad + h0] = m0;
-                s_m[warp * kHeadsPad + h0 + 1] = m1;
-                s_l[warp * kHeadsPad + h0] = l0;
-                s_l[warp * kHeadsPad + h0 + 1] = l1;
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int d = 4; d < 32; d <<= 1) {
+                l[nt][0] += __shfl_xor_sync(0xffffffffu, l[nt][0], d);
+                l[nt][1] += __shfl_xor_sync(0xffffffffu, l[nt][1], d);
             }
-            float* dst = s_o + (warp * kHeadsPad + h0) * kOPitch + (lane >> 2);
+            const int c0 = nt * 8 + 2 * (lane & 3);
+            if (lane < 4) {
+                s_m[warp * kCols + c0] = m[nt][0];
+                s_m[warp * kCols + c0 + 1] = m[nt][1];
+                s_l[warp * kCols + c0] = l[nt][0];
+                s_l[warp * kCols + c0 + 1] = l[nt][1];
+            }
+            float* dst = s_o + (warp * kCols + c0) * kOPitch + (lane >> 2);
 #pragma unroll
             for (int dt = 0; dt < 8; ++dt) {
-                dst[dt * 16] = o[dt][0];
-                dst[kOPitch + dt * 16] = o[dt][1];
-                dst[dt * 16 + 8] = o[dt][2];
-                dst[kOPitch + dt * 16 + 8] = o[dt][3];
+                dst[dt * 16] = o[nt][dt][0];
+                dst[kOPitch + dt * 16] = o[nt][dt][1];
+                dst[dt * 16 + 8] = o[nt][dt][2];
+                dst[kOPitch + dt * 16 + 8] = o[nt][dt][3];
             }
         }
         __syncthreads();
         {
             const bool final_out = (it.nsplits == 1) && a.always_partial == 0;
-            float* rec = a.workspace + (int64_t)item * group * (kHeadDim + 2);
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out) +
-                ((int64_t)it.b * a.num_q_heads + (int64_t)it.hk * group) * kHeadDim;
-            for (int idx = threadIdx.x; idx < group * kHeadDim; idx += WARPS * 32) {
+            // A record that does not fit the scratch is not written (lengths read from the
+            // device may have outgrown what the scratch was sized for).
+            const bool fits = final_out || item < a.item_capacity;
+            if (!fits && threadIdx.x == 0) raise_status(a, kStatusBadInput);
+            float* rec = a.workspace + (int64_t)item * cols * (kHeadDim + 2);
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
+            for (int idx = threadIdx.x; fits && idx < cols * kHeadDim; idx += WARPS * 32) {
                 const int n = idx >> 7;
                 const int d = idx & (kHeadDim - 1);
                 float mx = s_m[n];
 #pragma unroll
-                for (int w = 1; w < WARPS; ++w) mx = fmaxf(mx, s_m[w * kHeadsPad + n]);
+                for (int w = 1; w < WARPS; ++w) mx = fmaxf(mx, s_m[w * kCols + n]);
+                const float ref = safe_max(mx);
                 float acc = 0.0f, lsum = 0.0f;
 #pragma unroll
                 for (int w = 0; w < WARPS; ++w) {
-                    const float f = ex2_approx(s_m[w * kHeadsPad + n] - mx);
-                    acc += s_o[(w * kHeadsPad + n) * kOPitch + d] * f;
-                    lsum += s_l[w * kHeadsPad + n] * f;
+                    const float f = ex2_approx(s_m[w * kCols + n] - ref);
+                    acc += s_o[(w * kCols + n) * kOPitch + d] * f;
+                    lsum += s_l[w * kCols + n] * f;
                 }
                 if (final_out) {
-                    out[idx] = __float2bfloat16(acc / lsum);
+                    out[q_row_of(n) + d] = __float2bfloat16(acc / lsum);
                 } else {
                     rec[idx] = acc;
                     if (d == 0) {
-                        rec[group * kHeadDim + n] = mx;
-                        rec[group * kHeadDim + group + n] = lsum;
+                        rec[cols * kHeadDim + n] = mx;
+                        rec[cols * kHeadDim + cols + n] = lsum;
                     }
                 }
             }
         }
         __syncthreads();
     }
-    timeline_mark(4, a.fixed_block);
-    timeline_cta(3);
 }
 
-#ifdef GQA_TIMELINE
-__device__ unsigned long long g_timeline[64];
-__device__ unsigned long long g_cta_marks[4 * 1024];
-extern "C" int gqa_timeline_ctas(unsigned long long* host) {
-    return cudaMemcpyFromSymbol(host, g_cta_marks, sizeof(unsigned long long) * 4096) ==
-                   cudaSuccess ? 0 : -1;
-}
-extern "C" int gqa_timeline_read(unsigned long long* host64, int reset) {
-    if (cudaMemcpyFromSymbol(host64, g_timeline, sizeof(unsigned long long) * 64) != cudaSuccess) {
-        return -1;
-    }
-    if (reset) {
-        unsigned long long init[64];
-        for (int i = 0; i < 64; ++i) init[i] = (i & 1) ? 0ull : ~0ull;
-        if (cudaMemcpyToSymbol(g_timeline, init, sizeof(init)) != cudaSuccess) return -1;
-    }
-    return 0;
-}
-#endif
-
-size_t stream_bf16_smem_bytes(int warps, int stages, int keys, int batch_for_tables) {
+size_t stream_bf16_smem_bytes(int warps, int stages, int keys, int n_tiles, bool fused,
+                              int batch_for_tables) {
+    const size_t cols = 8 * (size_t)n_tiles;
     size_t bytes = 1024;  // alignment slack
     bytes += (size_t)warps * stages * keys * 512;
-    bytes += (size_t)warps * kHeadsPad * kOPitch * sizeof(float);
-    bytes += 2 * (size_t)warps * kHeadsPad * sizeof(float);
+    bytes += (size_t)warps * cols * kOPitch * sizeof(float);
+    bytes += 2 * (size_t)warps * cols * sizeof(float);
     bytes += (size_t)warps * stages * sizeof(uint64_t);
+    if (fused) bytes += cols * kQPitch * sizeof(__nv_bfloat16);
     bytes += 2 * ((size_t)batch_for_tables + 1) * sizeof(int32_t);
     return bytes;
 }
 
-template <int WARPS, int STAGES, int KEYS, int OCC>
+template <int WARPS, int STAGES, int KEYS, int OCC, int NT, bool FUSED>
 static cudaError_t launch_variant(const CUtensorMap& tk, const CUtensorMap& tv,
-                                  const DecodeArgs& args, int grid, cudaStream_t stream) {
+                                  const DecodeArgs& args, const FusedFrontArgs& ff, int grid,
+                                  cudaStream_t stream) {
     const int tables = args.seq_lens_dev != nullptr ? args.batch : 0;
-    const size_t smem = stream_bf16_smem_bytes(WARPS, STAGES, KEYS, tables);
-    auto kernel = gqa_decode_stream_bf16<WARPS, STAGES, KEYS, OCC>;
-    static size_t configured[64] = {};  // the attribute is per function and per device
+    const size_t smem = stream_bf16_smem_bytes(WARPS, STAGES, KEYS, NT, FUSED, tables);
+    auto kernel = gqa_decode_stream_bf16<WARPS, STAGES, KEYS, OCC, NT, FUSED>;
+    // The attribute is per function and per device.
+    static std::mutex mu;
+    static size_t configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || configured[dev] < smem) {
-        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = smem;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64 || configured[dev] < smem) {
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+            if (dev >= 0 && dev < 64) configured[dev] = smem;
+        }
     }
-    return launch_pdl(kernel, dim3(grid), dim3(WARPS * 32), smem, stream, tk, tv, args);
+    return launch_pdl(kernel, dim3(grid), dim3(WARPS * 32), smem, stream, tk, tv, args, ff);
 }
 
-cudaError_t launch_stream_bf16(const StreamShape& shape, const CUtensorMap& tk,
-                               const CUtensorMap& tv, const DecodeArgs& args, int grid,
-                               cudaStream_t stream) {
-#define GQA_VARIANT(W, S, K, O)                                                     \
-    if (shape.warps == W && shape.stages == S && shape.keys == K && shape.ctas_per_sm == O) { \
-        return launch_variant<W, S, K, O>(tk, tv, args, grid, stream);               \
+cudaError_t launch_stream_bf16(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeArgs& args,
+                               const FusedFrontArgs* fused, int grid, cudaStream_t stream) {
+    constexpr StreamShape S = kDefaultStreamShape;
+    FusedFrontArgs ff = {};
+    if (fused != nullptr) ff = *fused;
+    const int cols = args.group * args.q_tokens;
+    if (cols <= 8) {
+        return fused != nullptr
+                   ? launch_variant<S.warps, S.stages, S.keys, 1, 1, true>(tk, tv, args, ff, grid, stream)
+                   : launch_variant<S.warps, S.stages, S.keys, 1, 1, false>(tk, tv, args, ff, grid, stream);
     }
-    GQA_VARIANT(4, 1, 64, 1)
-    GQA_VARIANT(4, 2, 32, 1)
-    GQA_VARIANT(4, 3, 32, 1)
-    GQA_VARIANT(8, 1, 32, 1)
-    GQA_VARIANT(4, 1, 32, 2)
-#undef GQA_VARIANT
+    if (cols <= 16) {
+        return fused != nullptr
+                   ? launch_variant<S.warps, S.stages, S.keys, 1, 2, true>(tk, tv, args, ff, grid, stream)
+                   : launch_variant<S.warps, S.stages, S.keys, 1, 2, false>(tk, tv, args, ff, grid, stream);
+    }
     return cudaErrorInvalidValue;
 }
 

@@ -44,6 +44,11 @@ __device__ __forceinline__ const float* cache_row(const DecodeArgs& a, const voi
         const int32_t lb = t / a.block_tokens;
         tok = t - lb * a.block_tokens;
         blk = __ldg(a.block_table + (int64_t)b * a.blocks_per_seq + lb);
+        // A block id outside the cache is reported and read as block 0: no wild address.
+        if ((uint32_t)blk >= (uint32_t)a.num_blocks) {
+            if ((threadIdx.x & 31) == 0) raise_status(a, kStatusBadInput);
+            blk = 0;
+        }
     }
     return reinterpret_cast<const float*>(base) + (int64_t)blk * a.stride_block +
            (int64_t)tok * a.stride_token + (int64_t)hk * a.stride_head;
@@ -168,19 +173,22 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
         __syncthreads();
         {
             const bool final_out = (it.nsplits == 1) && a.always_partial == 0;
+            const bool fits = final_out || item < a.item_capacity;
+            if (!fits && threadIdx.x == 0) raise_status(a, kStatusBadInput);
             float* rec = a.workspace + (int64_t)item * group * (kHeadDim + 2);
             float* out = reinterpret_cast<float*>(a.out) +
                 ((int64_t)it.b * a.num_q_heads + (int64_t)it.hk * group) * kHeadDim;
-            for (int idx = threadIdx.x; idx < group * kHeadDim; idx += kF32Threads) {
+            for (int idx = threadIdx.x; fits && idx < group * kHeadDim; idx += kF32Threads) {
                 const int n = idx >> 7;
                 const int d = idx & (kHeadDim - 1);
                 float mx = s_m[0][n];
 #pragma unroll
                 for (int w = 1; w < kF32Warps; ++w) mx = fmaxf(mx, s_m[w][n]);
+                const float ref = safe_max(mx);
                 float acc = 0.f, lsum = 0.f;
 #pragma unroll
                 for (int w = 0; w < kF32Warps; ++w) {
-                    const float f = exp2f(s_m[w][n] - mx);
+                    const float f = exp2f(s_m[w][n] - ref);
                     acc += s_o[w][n][d] * f;
                     lsum += s_l[w][n] * f;
                 }
@@ -202,11 +210,33 @@ __global__ void __launch_bounds__(kF32Threads) gqa_decode_stream_f32(const Decod
 constexpr int kCombineLocal = 0;   // merge the splits of a unit
 constexpr int kCombineGather = 1;  // ... and exchange the finished rows (KV-head-parallel)
 constexpr int kCombineSeqPar = 2;  // ... and merge with the other ranks' slices of the keys
+constexpr int kCombineRecord = 3;  // ... and leave the row's record instead of the output
 constexpr int kCombineWideGrid = 160;  // largest grid that runs with 4 lanes per channel
 constexpr int kCombineTile = 32;   // splits merged per pass
 constexpr int kCombineSlots = 8;   // partial sums per channel per pass, whatever the CTA width
+constexpr int kRecWords = kHeadDim + 2;  // a row's record: 128 channel sums, maximum, row sum
 
-// One CTA per (sequence, query head) with LANES threads per output channel. The splits of a
+// Merges the records of `count` slices of one row's keys (each: channel sum d relative to the
+// slice's maximum, the maximum in the log2 domain, the row sum) in ascending order, so every
+// caller that holds the same records gets the same bits. A slice without keys has the record
+// (0, -inf, 0) and drops out. rec(r, w) returns word w of slice r.
+template <bool FAST_EXP, typename Rec>
+__device__ __forceinline__ float merge_slices(int count, int d, Rec rec) {
+    float m_all = rec(0, kHeadDim);
+    for (int r = 1; r < count; ++r) m_all = fmaxf(m_all, rec(r, kHeadDim));
+    const float ref = safe_max(m_all);
+    float l_all = 0.f, o_all = 0.f;
+    for (int r = 0; r < count; ++r) {
+        const float diff = rec(r, kHeadDim) - ref;
+        const float w = FAST_EXP ? ex2_approx(diff) : exp2f(diff);
+        l_all += rec(r, kHeadDim + 1) * w;
+        o_all += rec(r, d) * w;
+    }
+    return o_all / l_all;
+}
+
+// One CTA per output row (sequence, query token, query head) with LANES threads per output
+// channel. The splits of a
 // pass are dealt to 8 slots (split s goes to slot s % 8); a thread owns 8 / LANES slots and
 // adds each slot's splits in ascending order, then the slots are added in ascending order.
 // The result therefore does not depend on LANES, which is only a matter of how many threads
@@ -233,32 +263,42 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
     __shared__ float s_m[kCombineTile];
     __shared__ float s_l[kCombineTile];
     __shared__ float s_part[kCombineSlots][kHeadDim];
-    timeline_mark(5, a.fixed_block);
     pdl_launch_dependents();
     pdl_wait();
-    timeline_mark(6, a.fixed_block);
     const WorkTables tables = build_work_tables(a, s_tables);
-    const int32_t b = blockIdx.x / a.num_q_heads;
-    const int32_t h = blockIdx.x - b * a.num_q_heads;
+    // blockIdx.x = (sequence * q_tokens + token) * num_q_heads + head.
+    const int32_t bt = blockIdx.x / a.num_q_heads;
+    const int32_t h = blockIdx.x - bt * a.num_q_heads;
+    const int32_t b = bt / a.q_tokens;
     const int32_t group = a.group;
+    const int32_t cols = group * a.q_tokens;
     const int32_t hk = h / group;
-    const int32_t n = h - hk * group;
+    const int32_t col = (bt - b * a.q_tokens) * group + (h - hk * group);
     int32_t first, nsplits;
     unit_items(a, tables, b, hk, &first, &nsplits);
+    const bool records = MODE == kCombineSeqPar || MODE == kCombineRecord;
+    if ((nsplits > 1 || (records && nsplits == 1)) && first + nsplits > a.item_capacity) {
+        // The unit's records did not fit the scratch (the streaming kernel skipped them and
+        // raised the status word): nothing to read.
+        if (threadIdx.x == 0) raise_status(a, kStatusBadInput);
+        nsplits = 0;
+    }
     // Not split: the streaming kernel already wrote the final output.
     if (MODE == kCombineLocal && nsplits <= 1) return;
 
     const int d = threadIdx.x & (kHeadDim - 1);
     const int j = threadIdx.x >> 7;
-    const int64_t o_idx = ((int64_t)b * a.num_q_heads + h) * kHeadDim + d;
+    // The row's place in out: [sequence][token of the whole run][query head][channel].
+    const int64_t o_idx = (((int64_t)b * a.q_token_stride + a.q_token_first + (bt - b * a.q_tokens)) *
+                               a.num_q_heads + h) * kHeadDim + d;
     float result = 0.f;  // the finished channel, held by the threads with j == 0
     float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
-    if (nsplits > 1 || MODE == kCombineSeqPar) {
-        const int64_t rec_floats = (int64_t)group * (kHeadDim + 2);
+    if (nsplits > 1 || records) {
+        const int64_t rec_floats = (int64_t)cols * (kHeadDim + 2);
         const float* rec0 = a.workspace + (int64_t)first * rec_floats;
-        const float* m_base = rec0 + group * kHeadDim + n;
-        const float* l_base = m_base + group;
-        const float* o_base = rec0 + n * kHeadDim + d;
+        const float* m_base = rec0 + cols * kHeadDim + col;
+        const float* l_base = m_base + cols;
+        const float* o_base = rec0 + col * kHeadDim + d;
 
         for (int32_t base = 0; base < nsplits; base += kCombineTile) {
             const int32_t cnt = min(kCombineTile, nsplits - base);
@@ -293,10 +333,12 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
             float tmax = s_m[0];
             for (int32_t i = 1; i < cnt; ++i) tmax = fmaxf(tmax, s_m[i]);
             const float m_new = fmaxf(m_run, tmax);
-            const float rescale = BF16_OUT ? ex2_approx(m_run - m_new) : exp2f(m_run - m_new);
+            // A split whose keys are all hidden from this row's token has m = -inf, l = 0.
+            const float ref = safe_max(m_new);
+            const float rescale = BF16_OUT ? ex2_approx(m_run - ref) : exp2f(m_run - ref);
             float ltile = 0.f;
             for (int32_t i = 0; i < cnt; ++i) {
-                const float w = BF16_OUT ? ex2_approx(s_m[i] - m_new) : exp2f(s_m[i] - m_new);
+                const float w = BF16_OUT ? ex2_approx(s_m[i] - ref) : exp2f(s_m[i] - ref);
                 ltile += s_l[i] * w;
             }
 #pragma unroll
@@ -306,7 +348,7 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
                 for (int r = 0; r < kPerSlot; ++r) {
                     const int32_t s = (j + t * LANES) + r * kCombineSlots;
                     if (s < cnt) {
-                        const float w = BF16_OUT ? ex2_approx(s_m[s] - m_new) : exp2f(s_m[s] - m_new);
+                        const float w = BF16_OUT ? ex2_approx(s_m[s] - ref) : exp2f(s_m[s] - ref);
                         part += o[t][r] * w;
                     }
                 }
@@ -323,8 +365,7 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
             m_run = m_new;
             __syncthreads();  // the next pass overwrites s_m, s_l and s_part
         }
-        timeline_mark(7, a.fixed_block);
-        if (j == 0 && MODE != kCombineSeqPar) {
+        if (j == 0 && !records) {
             result = acc / l_run;
             if (BF16_OUT) {
                 reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(result);
@@ -337,6 +378,16 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
                           : __ldcg(reinterpret_cast<const float*>(a.out) + o_idx);
     }
     if (MODE == kCombineLocal) return;
+    if (MODE == kCombineRecord) {
+        // The row's record goes to the caller, who merges it with other slices' records.
+        float* dst = reinterpret_cast<float*>(g.recv) + (int64_t)blockIdx.x * kRecWords;
+        if (j == 0) dst[d] = acc;
+        if (threadIdx.x == 0) {
+            dst[kHeadDim] = m_run;
+            dst[kHeadDim + 1] = l_run;
+        }
+        return;
+    }
 
     // ---- exchange with the other ranks ----
     __shared__ uint32_t s_step;
@@ -384,10 +435,9 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
             }
         }
     } else {
-        // Sequence-parallel: this rank saw a slice of the row's keys. Its record (128 channel
-        // sums relative to its maximum, the maximum, the row sum) goes to every other rank; the
-        // records of all ranks are merged in rank order, so every rank gets the same bits.
-        constexpr int kRecWords = kHeadDim + 2;
+        // Sequence-parallel: this rank saw a slice of the row's keys. Its record goes to every
+        // other rank; the records of all ranks are merged in rank order, so every rank gets the
+        // same bits.
         __shared__ uint32_t s_rec[kMaxPeers][kRecWords];
         if (j == 0) s_rec[g.rank][d] = __float_as_uint(acc);
         if (threadIdx.x == 0) {
@@ -421,21 +471,12 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
         if (timed_out) s_timed_out = 1;
         __syncthreads();
         if (j == 0 && s_timed_out == 0) {
-            float m_all = __uint_as_float(s_rec[0][kHeadDim]);
-            for (int r = 1; r < g.nranks; ++r) {
-                m_all = fmaxf(m_all, __uint_as_float(s_rec[r][kHeadDim]));
-            }
-            float l_all = 0.f, o_all = 0.f;
-            for (int r = 0; r < g.nranks; ++r) {
-                const float diff = __uint_as_float(s_rec[r][kHeadDim]) - m_all;
-                const float w = BF16_OUT ? ex2_approx(diff) : exp2f(diff);
-                l_all += __uint_as_float(s_rec[r][kHeadDim + 1]) * w;
-                o_all += __uint_as_float(s_rec[r][d]) * w;
-            }
+            const float merged = merge_slices<BF16_OUT>(
+                g.nranks, d, [&](int r, int w) { return __uint_as_float(s_rec[r][w]); });
             if (BF16_OUT) {
-                reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(o_all / l_all);
+                reinterpret_cast<__nv_bfloat16*>(a.out)[o_idx] = __float2bfloat16(merged);
             } else {
-                reinterpret_cast<float*>(a.out)[o_idx] = o_all / l_all;
+                reinterpret_cast<float*>(a.out)[o_idx] = merged;
             }
         }
     }
@@ -444,7 +485,7 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
     if (threadIdx.x == 0) {
         if (s_timed_out) {
             ctrl->status = 1;
-            if (g.status != nullptr) atomicExch(g.status, 2);
+            if (g.status != nullptr) atomicExch(g.status, kStatusPeerTimeout);
         }
         // The last CTA to finish advances the step counter for the next launch.
         __threadfence();
@@ -454,6 +495,36 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
             ctrl->step = s_step;
         }
     }
+}
+
+// Stand-alone merge of slice records (what the sequence-parallel exchange does after the
+// records have arrived): records [nparts][rows][130], one thread per output channel.
+template <bool BF16_OUT>
+__global__ void __launch_bounds__(kHeadDim)
+    gqa_merge_partials_kernel(const float* __restrict__ records, int32_t nparts, int64_t rows,
+                              void* out) {
+    const int64_t row = blockIdx.x;
+    const int d = threadIdx.x;
+    const float merged = merge_slices<BF16_OUT>(nparts, d, [&](int r, int w) {
+        return __ldg(records + ((int64_t)r * rows + row) * kRecWords + w);
+    });
+    if (BF16_OUT) {
+        reinterpret_cast<__nv_bfloat16*>(out)[row * kHeadDim + d] = __float2bfloat16(merged);
+    } else {
+        reinterpret_cast<float*>(out)[row * kHeadDim + d] = merged;
+    }
+}
+
+cudaError_t launch_merge_partials(const float* records, int32_t nparts, int64_t rows,
+                                  bool bf16_out, void* out, cudaStream_t stream) {
+    if (bf16_out) {
+        gqa_merge_partials_kernel<true><<<(unsigned)rows, kHeadDim, 0, stream>>>(records, nparts,
+                                                                                rows, out);
+    } else {
+        gqa_merge_partials_kernel<false><<<(unsigned)rows, kHeadDim, 0, stream>>>(records, nparts,
+                                                                                 rows, out);
+    }
+    return cudaGetLastError();
 }
 
 cudaError_t launch_stream_f32(const DecodeArgs& args, int grid, cudaStream_t stream) {
@@ -468,10 +539,10 @@ cudaError_t launch_stream_f32(const DecodeArgs& args, int grid, cudaStream_t str
 }
 
 cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t stream,
-                           const PeerGatherArgs* gather, bool sequence_parallel) {
+                           const PeerGatherArgs* gather, CombineKind kind) {
     const size_t smem =
         args.seq_lens_dev != nullptr ? 2 * ((size_t)args.batch + 1) * sizeof(int32_t) : 0;
-    const int grid = args.batch * args.num_q_heads;
+    const int grid = args.batch * args.q_tokens * args.num_q_heads;
     const bool wide = grid <= kCombineWideGrid;
     PeerGatherArgs g;
     std::memset(&g, 0, sizeof(g));
@@ -486,18 +557,39 @@ cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t s
                                    stream, args, g)                                             \
                       : launch_pdl(gqa_decode_combine<false, 2, MODE>, dim3(grid), block, smem, \
                                    stream, args, g)))
-    if (gather != nullptr && sequence_parallel) return GQA_COMBINE(kCombineSeqPar);
-    if (gather != nullptr) {
-        if (!wide) return cudaErrorInvalidValue;  // the caller checks combine_can_gather()
-        return GQA_COMBINE(kCombineGather);
+    switch (kind) {
+        case CombineKind::kSeqPar:
+            if (gather == nullptr) return cudaErrorInvalidValue;
+            return GQA_COMBINE(kCombineSeqPar);
+        case CombineKind::kRecord:
+            if (gather == nullptr) return cudaErrorInvalidValue;
+            return GQA_COMBINE(kCombineRecord);
+        case CombineKind::kGather:
+            if (gather == nullptr || !wide) return cudaErrorInvalidValue;  // combine_can_gather()
+            return GQA_COMBINE(kCombineGather);
+        case CombineKind::kLocal:
+            break;
     }
     return GQA_COMBINE(kCombineLocal);
 #undef GQA_COMBINE
 }
 
-bool combine_can_gather(int batch, int num_q_heads, int sm_count) {
-    const int grid = batch * num_q_heads;
-    return grid <= kCombineWideGrid && grid <= sm_count;
+// CTAs of the combine kernel that one SM holds at once for a grid of this size (the exchange
+// modes make every CTA wait for its peers, so the whole grid must be resident).
+int combine_resident_ctas(int grid, int sm_count) {
+    const bool wide = grid <= kCombineWideGrid;
+    int per_sm = 0;
+    const cudaError_t e =
+        wide ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                   &per_sm, gqa_decode_combine<true, 4, kCombineSeqPar>, kHeadDim * 4, 0)
+             : cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                   &per_sm, gqa_decode_combine<true, 2, kCombineSeqPar>, kHeadDim * 2, 0);
+    if (e != cudaSuccess) return 0;
+    return per_sm * sm_count;
+}
+
+bool combine_can_gather(int rows, int sm_count) {
+    return rows <= kCombineWideGrid && rows <= sm_count;
 }
 
 }  // namespace gqa

@@ -13,7 +13,7 @@ namespace gqa {
 
 // Shape of the BF16 streaming kernel: warps per CTA (each with its own staging ring), stages
 // per ring, keys per stage and CTAs resident per SM. Each CTA keeps
-// warps * stages * keys * 512 bytes of K/V in flight.
+// warps * stages * keys * 512 bytes of K/V in flight (128 KiB per SM measured best).
 struct StreamShape {
     int warps;
     int stages;
@@ -22,30 +22,57 @@ struct StreamShape {
 };
 constexpr StreamShape kDefaultStreamShape = {4, 1, 64, 1};
 
-size_t stream_bf16_smem_bytes(int warps, int stages, int keys, int batch_for_tables);
+size_t stream_bf16_smem_bytes(int warps, int stages, int keys, int n_tiles, bool fused,
+                              int batch_for_tables);
 
-// The tensor maps must have been encoded with a box of `shape.keys` rows.
-cudaError_t launch_stream_bf16(const StreamShape& shape, const CUtensorMap& tmap_k,
-                               const CUtensorMap& tmap_v, const DecodeArgs& args, int grid,
+// What the BF16 streaming kernel needs to run the front stage itself (QK-Norm + RoPE of the
+// raw query rows in DecodeArgs::q, and of the new key rows, which it appends to the cache
+// together with the value rows). Token t of sequence b sits at position len_b - q_tokens + t.
+struct FusedFrontArgs {
+    const void* k_new;      // [batch][q_tokens][num_kv_heads][128] raw keys
+    const void* v_new;      // same shape
+    const void* qk_weight;  // [2][128]: query norm weights, key norm weights
+    void* q_out;            // optional: the rotated queries, laid out like q
+    const float* sin_cache; // [table_len][64] or null (angles computed in the kernel)
+    const float* cos_cache;
+    int32_t table_len;
+    float eps;
+};
+
+// The tensor maps must have been encoded with a box of kDefaultStreamShape.keys rows. With
+// `fused` the kernel also runs the front stage (see FusedFrontArgs). group * q_tokens <= 16.
+cudaError_t launch_stream_bf16(const CUtensorMap& tmap_k, const CUtensorMap& tmap_v,
+                               const DecodeArgs& args, const FusedFrontArgs* fused, int grid,
                                cudaStream_t stream);
 
 cudaError_t launch_stream_f32(const DecodeArgs& args, int grid, cudaStream_t stream);
 
 struct PeerGatherArgs;
 
-// One CTA per (sequence, query head); merges the partial records of split units. With
-// `gather` the same kernel also exchanges the finished rows with the other ranks of a
-// KV-head-parallel node through their peer windows (allowed when combine_can_gather()).
-// With `sequence_parallel` (and `gather`) the rows are instead merged with the records the
-// other ranks computed on their slices of the keys.
+// One CTA per output row (sequence, query token, query head); merges the partial records of
+// split units.
+//   kLocal   writes the finished rows of split units to DecodeArgs::out;
+//   kGather  also exchanges the finished rows with the other ranks of a KV-head-parallel node
+//            through the peer windows in `gather` (allowed when combine_can_gather());
+//   kSeqPar  merges the row with the records the other ranks computed on their slices of the
+//            keys (records travel through the peer windows in `gather`);
+//   kRecord  leaves the row's record (128 channel sums, maximum, row sum) in gather->recv
+//            ([rows][130] floats) instead of an output row.
+enum class CombineKind { kLocal, kGather, kSeqPar, kRecord };
 cudaError_t launch_combine(const DecodeArgs& args, bool bf16_out, cudaStream_t stream,
                            const PeerGatherArgs* gather = nullptr,
-                           bool sequence_parallel = false);
-bool combine_can_gather(int batch, int num_q_heads, int sm_count);
+                           CombineKind kind = CombineKind::kLocal);
+bool combine_can_gather(int rows, int sm_count);
+int combine_resident_ctas(int grid, int sm_count);
+
+// out[row] = merge of records[part][row] over the parts, in ascending order.
+cudaError_t launch_merge_partials(const float* records, int32_t nparts, int64_t rows,
+                                  bool bf16_out, void* out, cudaStream_t stream);
 
 // gqa_decode with the gather fused into the combine kernel when that is possible; *fused
 // tells whether it was (if not, nothing was exchanged and the caller gathers separately).
-int decode_with_gather(const gqa_decode_params* p, const PeerGatherArgs* gather, bool* fused);
+int decode_with_gather(const gqa_decode_params* p, const gqa_fused_front* front,
+                       const PeerGatherArgs* gather, bool* fused);
 
 // Sequence-parallel decode: p describes this rank's slice of every sequence (all heads); the
 // combine kernel merges the ranks' records through the peer windows and writes the complete
@@ -80,6 +107,11 @@ struct FrontArgs {
     int32_t block_tokens;
     int32_t fixed_block;
     int32_t k_in_place;  // k_new already is the cache row: rotate it where it lies
+    int32_t q_tokens;      // new tokens per sequence, at consecutive positions
+    int32_t pos_capacity;  // positions a sequence can hold
+    int32_t table_len;     // rows of the sin/cos tables
+    int32_t num_blocks;    // blocks in the cache
+    int32_t* status;       // raised when a device-side position or block id is out of range
     float eps;
 };
 

@@ -24,6 +24,7 @@ using gqa::kChunkKeys;
 using gqa::kHeadDim;
 
 constexpr int kMaxGroup = 8;
+constexpr int kMaxColumns = 16;  // (query token, query head) columns per unit and launch
 constexpr int kPlanWarps = 4;  // warps sharing an item in both streaming kernels
 
 size_t dtype_bytes(int32_t dtype) { return dtype == GQA_DTYPE_F32 ? 4 : 2; }
@@ -41,14 +42,30 @@ int validate_layout(const gqa_kv_layout& l, int32_t dtype, int32_t num_kv_heads)
     return GQA_OK;
 }
 
-// Everything that can be checked without touching device memory.
-int validate_decode(const gqa_decode_params* p) {
+int32_t tokens_of(const gqa_decode_params* p) { return p->q_tokens > 0 ? p->q_tokens : 1; }
+
+int64_t capacity_of(const gqa_decode_params* p) {
+    return p->block_table_dev != nullptr ? (int64_t)p->blocks_per_seq * p->layout.block_tokens
+                                         : p->layout.block_tokens;
+}
+
+// Everything that can be checked without touching device memory. allow_empty: a sequence may
+// have no key at all (an empty slice of a sequence-parallel rank).
+int validate_decode(const gqa_decode_params* p, bool allow_empty = false, bool in_passes = false) {
     if (p == nullptr) return GQA_ERR_NULL;
     if (p->dtype != GQA_DTYPE_F32 && p->dtype != GQA_DTYPE_BF16) return GQA_ERR_DTYPE;
     if (p->batch <= 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0) return GQA_ERR_SHAPE;
     if (p->head_dim != kHeadDim) return GQA_ERR_SHAPE;
     if (p->num_q_heads % p->num_kv_heads != 0) return GQA_ERR_SHAPE;
     if (p->num_q_heads / p->num_kv_heads > kMaxGroup) return GQA_ERR_UNSUPPORTED;
+    if (p->q_tokens < 0) return GQA_ERR_SHAPE;
+    const int32_t tokens = tokens_of(p);
+    if (tokens > 1) {
+        if (p->dtype != GQA_DTYPE_BF16) return GQA_ERR_UNSUPPORTED;
+        if (!in_passes && tokens * (p->num_q_heads / p->num_kv_heads) > kMaxColumns) {
+            return GQA_ERR_UNSUPPORTED;
+        }
+    }
     int rc = validate_layout(p->layout, p->dtype, p->num_kv_heads);
     if (rc != GQA_OK) return rc;
     if (p->q == nullptr || p->k_cache == nullptr || p->v_cache == nullptr || p->out == nullptr) {
@@ -73,7 +90,8 @@ int validate_decode(const gqa_decode_params* p) {
     if (p->seq_lens_host != nullptr) {
         for (int32_t b = 0; b < p->batch; ++b) {
             const int32_t len = p->seq_lens_host[b];
-            if (len <= 0 || len > capacity) return GQA_ERR_RANGE;
+            if (len == 0 && allow_empty && p->seq_lens_dev != nullptr) continue;
+            if (len < tokens || len > capacity) return GQA_ERR_RANGE;
             if (p->seq_lens_dev == nullptr && len != p->seq_lens_host[0]) return GQA_ERR_UNSUPPORTED;
         }
     } else if (p->batch > gqa::kMaxRaggedBatch) {
@@ -104,22 +122,7 @@ int device_sm_count(int32_t* out) {
     return GQA_OK;
 }
 
-// Kernel shape; GQA_STREAM_SHAPE="warps,stages,keys[,ctas_per_sm]" overrides it for tuning runs.
-gqa::StreamShape stream_shape() {
-    static gqa::StreamShape shape = [] {
-        gqa::StreamShape s = gqa::kDefaultStreamShape;
-        const char* env = std::getenv("GQA_STREAM_SHAPE");
-        int w = 0, st = 0, k = 0, occ = 1;
-        if (env != nullptr && std::sscanf(env, "%d,%d,%d,%d", &w, &st, &k, &occ) >= 3) {
-            s.warps = w;
-            s.stages = st;
-            s.keys = k;
-            s.ctas_per_sm = occ;
-        }
-        return s;
-    }();
-    return shape;
-}
+gqa::StreamShape stream_shape() { return gqa::kDefaultStreamShape; }
 
 // ---- split planning ------------------------------------------------------------------------
 // Cost of a candidate, in "steps": one step is every warp of a CTA consuming one chunk.
@@ -174,14 +177,14 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
     const size_t rec = record_bytes(in.group);
 
     auto finish = [&](int32_t q) -> int {
-        q = ceil_div(q, in.chunk_align) * in.chunk_align;
+        q = ceil_div(q < 1 ? 1 : q, in.chunk_align) * in.chunk_align;
         int32_t ms = 0;
         const int64_t items = items_for(in, q, &ms);
         if (items > INT32_MAX) return GQA_ERR_SHAPE;
         out->split_chunks = q;
         out->max_splits = ms;
         out->num_items = (int32_t)items;
-        out->num_ctas = (int32_t)(items < g_max ? items : g_max);
+        out->num_ctas = (int32_t)(items < g_max ? (items > 0 ? items : 1) : g_max);
         out->needs_combine = ms > 1 ? 1 : 0;
         out->reserved = 0;
         out->workspace_bytes = ms > 1 ? (size_t)items * rec : 0;
@@ -192,6 +195,7 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
     };
 
     if (in.split_keys > 0) return finish(ceil_div(in.split_keys, kChunkKeys));
+    if (max_chunks == 0) return finish(1);  // nothing but empty slices
 
     // Candidates: q = ceil(max_chunks / s) for s = 1, 2, ... while the grid is not yet
     // oversubscribed eight times; evaluated with the uniform upper bound on item size.
@@ -225,13 +229,11 @@ int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pl
     PlanInput in;
     in.batch = p->batch;
     in.num_kv_heads = p->num_kv_heads;
-    in.group = p->num_q_heads / p->num_kv_heads;
+    in.group = (p->num_q_heads / p->num_kv_heads) * tokens_of(p);  // columns of a record
     in.lens = p->seq_lens_host;
     in.uniform_len = 0;
+    const int64_t capacity = capacity_of(p);
     if (in.lens == nullptr) {
-        const int64_t capacity = p->block_table_dev != nullptr
-                                     ? (int64_t)p->blocks_per_seq * p->layout.block_tokens
-                                     : p->layout.block_tokens;
         in.uniform_len = p->plan_len_hint > 0 ? p->plan_len_hint : (int32_t)capacity;
     }
     in.sm_count = sm_count * (p->dtype == GQA_DTYPE_BF16 ? stream_shape().ctas_per_sm : 1);
@@ -247,28 +249,44 @@ int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pl
         p->layout.block_tokens % stage_keys != 0) {
         return GQA_ERR_SHAPE;
     }
-    int rc = make_plan(in, out);
+    const int32_t g_max = in.max_ctas > 0 && in.max_ctas < in.sm_count ? in.max_ctas : in.sm_count;
+    if (p->seq_lens_host != nullptr || p->seq_lens_dev == nullptr) {
+        int rc = make_plan(in, out);
+        if (rc != GQA_OK) return rc;
+        if (p->seq_lens_dev != nullptr && p->workspace != nullptr &&
+            ceil_div((int32_t)capacity, kChunkKeys) > out->split_chunks) {
+            // The kernels follow the device lengths: keep the combine launch whenever a
+            // sequence could be split, so that the launch sequence does not depend on them.
+            out->needs_combine = 1;
+        }
+        return GQA_OK;
+    }
+    // Lengths are only known on the device: the split comes from the hint, the scratch is
+    // sized for full sequences; a split too fine for the caller's scratch is coarsened.
+    PlanInput hint = in;
+    hint.workspace_bytes = 0;
+    int rc = make_plan(hint, out);
     if (rc != GQA_OK) return rc;
-    if (p->seq_lens_host == nullptr) {
-        // Lengths are only known on the device: size the scratch for full sequences.
-        PlanInput full = in;
-        const int64_t capacity = p->block_table_dev != nullptr
-                                     ? (int64_t)p->blocks_per_seq * p->layout.block_tokens
-                                     : p->layout.block_tokens;
-        full.uniform_len = (int32_t)capacity;
-        full.split_keys = out->split_chunks * kChunkKeys;
+    PlanInput full = in;
+    full.uniform_len = (int32_t)capacity;
+    int32_t chunks = out->split_chunks;
+    const int32_t cap_chunks = ceil_div((int32_t)capacity, kChunkKeys);
+    for (;;) {
+        full.split_keys = chunks * kChunkKeys;
         gqa_decode_plan_info upper;
         rc = make_plan(full, &upper);
-        if (rc != GQA_OK) return rc;
-        out->num_items = upper.num_items;
-        out->max_splits = upper.max_splits;
-        out->needs_combine = upper.needs_combine;
-        out->workspace_bytes = upper.workspace_bytes;
-        const int32_t g_max =
-            in.max_ctas > 0 && in.max_ctas < in.sm_count ? in.max_ctas : in.sm_count;
-        out->num_ctas = upper.num_items < g_max ? upper.num_items : g_max;
+        if (rc == GQA_OK) {
+            out->split_chunks = upper.split_chunks;
+            out->num_items = upper.num_items;
+            out->max_splits = upper.max_splits;
+            out->needs_combine = upper.needs_combine;
+            out->workspace_bytes = upper.workspace_bytes;
+            out->num_ctas = upper.num_items < g_max ? upper.num_items : g_max;
+            return GQA_OK;
+        }
+        if (rc != GQA_ERR_WORKSPACE || p->split_keys > 0 || chunks >= cap_chunks) return rc;
+        chunks *= 2;
     }
-    return GQA_OK;
 }
 
 // ---- tensor maps ------------------------------------------------------------------------------
@@ -383,8 +401,15 @@ gqa_kv_layout clean_layout(const gqa_kv_layout& l) {
 }  // namespace
 
 namespace {
-int decode_impl(const gqa_decode_params* p, const gqa::PeerGatherArgs* gather,
-                bool sequence_parallel, bool* fused);
+enum class DecodeMode { kOutput, kSeqPar, kRecords };
+// A launch may cover tokens [first, first + count) of the q_tokens of each sequence.
+struct TokenPass {
+    int32_t first;
+    int32_t count;
+};
+int decode_impl(const gqa_decode_params* p, const gqa_fused_front* front,
+                const gqa::PeerGatherArgs* gather, DecodeMode mode, float* records, bool* fused,
+                const TokenPass* pass = nullptr);
 }  // namespace
 
 int gqa::cached_matrix_map(const void* base, int64_t cols, int64_t rows, int64_t pitch,
@@ -486,52 +511,126 @@ int gqa_layout_pool(int32_t num_blocks, int32_t block_tokens, int32_t num_kv_hea
 
 int gqa_decode_plan(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out) {
     if (out == nullptr) return GQA_ERR_NULL;
-    int rc = validate_decode(p);
+    int rc = validate_decode(p, false, true);
     if (rc != GQA_OK) return rc;
     if (sm_count <= 0) {
         rc = device_sm_count(&sm_count);
         if (rc != GQA_OK) return rc;
     }
-    return plan_from_params(p, sm_count, out);
+    // More (token, head) columns than one launch holds run as several passes: plan one pass.
+    gqa_decode_params planned = *p;
+    const int32_t per_pass = kMaxColumns / (p->num_q_heads / p->num_kv_heads);
+    if (tokens_of(p) > per_pass) planned.q_tokens = per_pass;
+    return plan_from_params(&planned, sm_count, out);
 }
 
-int gqa_decode(const gqa_decode_params* p) { return gqa::decode_with_gather(p, nullptr, nullptr); }
+int gqa_decode(const gqa_decode_params* p) {
+    return gqa::decode_with_gather(p, nullptr, nullptr, nullptr);
+}
+
+int gqa_decode_fused(const gqa_decode_params* p, const gqa_fused_front* front) {
+    if (front == nullptr) return GQA_ERR_NULL;
+    return gqa::decode_with_gather(p, front, nullptr, nullptr);
+}
+
+int gqa_decode_partial(const gqa_decode_params* p, float* records) {
+    if (records == nullptr) return GQA_ERR_NULL;
+    if (!aligned16(records)) return GQA_ERR_ALIGN;
+    return decode_impl(p, nullptr, nullptr, DecodeMode::kRecords, records, nullptr);
+}
+
+int gqa_merge_partials(const float* records, int32_t nparts, int64_t rows, int32_t head_dim,
+                       int32_t dtype, void* out, void* stream) {
+    if (records == nullptr || out == nullptr) return GQA_ERR_NULL;
+    if (dtype != GQA_DTYPE_F32 && dtype != GQA_DTYPE_BF16) return GQA_ERR_DTYPE;
+    if (head_dim != kHeadDim || nparts <= 0 || rows <= 0 || rows > INT32_MAX) return GQA_ERR_SHAPE;
+    const cudaError_t e = gqa::launch_merge_partials(records, nparts, rows, dtype == GQA_DTYPE_BF16,
+                                                     out, reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? GQA_OK : GQA_ERR_CUDA;
+}
 
 }  // extern "C"
 
-int gqa::decode_with_gather(const gqa_decode_params* p, const gqa::PeerGatherArgs* gather,
-                            bool* fused) {
-    return decode_impl(p, gather, false, fused);
+int gqa::decode_with_gather(const gqa_decode_params* p, const gqa_fused_front* front,
+                            const gqa::PeerGatherArgs* gather, bool* fused) {
+    if (p != nullptr && p->num_kv_heads > 0 && p->q_tokens > 1 &&
+        p->q_tokens * (p->num_q_heads / p->num_kv_heads) > kMaxColumns &&
+        p->num_q_heads / p->num_kv_heads <= kMaxGroup && gather == nullptr) {
+        // More (token, head) columns than one launch holds: several passes over the cache, each
+        // over the next tokens. A later pass may not prefetch early: the pass before it may
+        // still be appending its tokens' rows.
+        const int32_t per_pass = kMaxColumns / (p->num_q_heads / p->num_kv_heads);
+        gqa_decode_params local = *p;
+        for (int32_t first = 0; first < p->q_tokens; first += per_pass) {
+            const TokenPass pass = {first, p->q_tokens - first < per_pass ? p->q_tokens - first
+                                                                          : per_pass};
+            if (first > 0) local.early_prefetch = 0;
+            const int rc = decode_impl(&local, front, nullptr, DecodeMode::kOutput, nullptr,
+                                       nullptr, &pass);
+            if (rc != GQA_OK) return rc;
+        }
+        if (fused != nullptr) *fused = false;
+        return GQA_OK;
+    }
+    return decode_impl(p, front, gather, DecodeMode::kOutput, nullptr, fused);
 }
 
 int gqa::decode_sequence_parallel(const gqa_decode_params* p, const gqa::PeerGatherArgs* gather) {
     if (gather == nullptr) return GQA_ERR_NULL;
-    return decode_impl(p, gather, true, nullptr);
+    return decode_impl(p, nullptr, gather, DecodeMode::kSeqPar, nullptr, nullptr);
 }
 
 namespace {
 
-int decode_impl(const gqa_decode_params* p, const gqa::PeerGatherArgs* gather,
-                bool sequence_parallel, bool* fused) {
+int decode_impl(const gqa_decode_params* p, const gqa_fused_front* front,
+                const gqa::PeerGatherArgs* gather, DecodeMode mode, float* records, bool* fused,
+                const TokenPass* pass) {
     if (fused != nullptr) *fused = false;
-    int rc = validate_decode(p);
+    const bool by_records = mode != DecodeMode::kOutput;
+    int rc = validate_decode(p, by_records, pass != nullptr);
     if (rc != GQA_OK) return rc;
+    const int32_t all_tokens = tokens_of(p);
+    const int32_t tokens = pass != nullptr ? pass->count : all_tokens;
+    // Tokens of later passes are not attended by this one: its sequences end before them.
+    const int32_t len_offset = pass != nullptr ? all_tokens - pass->first - pass->count : 0;
+    if (by_records && tokens > 1) return GQA_ERR_UNSUPPORTED;
+    if (front != nullptr) {
+        if (p->dtype != GQA_DTYPE_BF16 || by_records) return GQA_ERR_UNSUPPORTED;
+        if (front->k_new == nullptr || front->v_new == nullptr || front->qk_weight == nullptr) {
+            return GQA_ERR_NULL;
+        }
+        if ((front->sin_cache == nullptr) != (front->cos_cache == nullptr)) return GQA_ERR_NULL;
+        if (front->sin_cache != nullptr && front->table_len <= 0) return GQA_ERR_RANGE;
+        if (!aligned16(front->k_new) || !aligned16(front->v_new)) return GQA_ERR_ALIGN;
+        // Every CTA of a unit reads the raw rows: they cannot be rotated in place.
+        if (front->q_out == p->q) return GQA_ERR_UNSUPPORTED;
+    }
     int32_t sms = 0;
     rc = device_sm_count(&sms);
     if (rc != GQA_OK) return rc;
     gqa_decode_plan_info plan;
-    rc = plan_from_params(p, sms, &plan);
+    {
+        gqa_decode_params planned = *p;
+        planned.q_tokens = tokens;
+        rc = plan_from_params(&planned, sms, &plan);
+    }
     if (rc != GQA_OK) return rc;
-    if (sequence_parallel && !plan.needs_combine) {
-        // Every unit leaves a record for the merge across ranks, also when it is not split.
+    const int32_t group = p->num_q_heads / p->num_kv_heads;
+    const size_t rec_bytes = (size_t)group * tokens * (kHeadDim + 2) * sizeof(float);
+    if (by_records && !plan.needs_combine) {
+        // Every unit leaves a record for the merge across slices, also when it is not split.
         plan.needs_combine = 1;
-        plan.workspace_bytes = (size_t)plan.num_items * (p->num_q_heads / p->num_kv_heads) *
-                               (kHeadDim + 2) * sizeof(float);
+        plan.workspace_bytes = (size_t)plan.num_items * rec_bytes;
     }
     if (plan.needs_combine) {
         if (p->workspace == nullptr) return GQA_ERR_NULL;
         if (p->workspace_bytes < plan.workspace_bytes) return GQA_ERR_WORKSPACE;
         if (!aligned16(p->workspace)) return GQA_ERR_ALIGN;
+    }
+    const int rows = p->batch * tokens * p->num_q_heads;
+    if (mode == DecodeMode::kSeqPar && rows > gqa::combine_resident_ctas(rows, sms)) {
+        // Every CTA of the merge waits for its peers' records: the grid must be resident.
+        return GQA_ERR_UNSUPPORTED;
     }
 
     gqa::DecodeArgs a;
@@ -550,14 +649,22 @@ int decode_impl(const gqa_decode_params* p, const gqa::PeerGatherArgs* gather,
     a.batch = p->batch;
     a.num_q_heads = p->num_q_heads;
     a.num_kv_heads = p->num_kv_heads;
-    a.group = p->num_q_heads / p->num_kv_heads;
-    a.uniform_len = p->seq_lens_dev == nullptr ? p->seq_lens_host[0] : 0;
+    a.group = group;
+    a.uniform_len = p->seq_lens_dev == nullptr ? p->seq_lens_host[0] - len_offset : 0;
     a.split_chunks = plan.split_chunks;
     a.blocks_per_seq = p->blocks_per_seq;
     a.block_tokens = p->layout.block_tokens;
     a.fixed_block = p->fixed_block;
     a.early_prefetch = p->early_prefetch ? 1 : 0;
-    a.always_partial = sequence_parallel ? 1 : 0;
+    a.always_partial = by_records ? 1 : 0;
+    a.q_tokens = tokens;
+    a.q_token_stride = all_tokens;
+    a.q_token_first = pass != nullptr ? pass->first : 0;
+    a.len_offset = len_offset;
+    a.len_capacity = (int32_t)capacity_of(p);
+    const size_t fit = p->workspace != nullptr ? p->workspace_bytes / rec_bytes : 0;
+    a.item_capacity = fit > (size_t)INT32_MAX ? INT32_MAX : (int32_t)fit;
+    a.num_blocks = p->layout.num_blocks;
     a.scale_log2 = (1.0f / sqrtf((float)kHeadDim)) * 1.44269504088896340736f;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(p->stream);
 
@@ -572,18 +679,40 @@ int decode_impl(const gqa_decode_params* p, const gqa::PeerGatherArgs* gather,
         rc = cached_cache_map(p->v_cache, lay, p->num_kv_heads, shape.keys, &head_first, &tv);
         if (rc != GQA_OK) return rc;
         a.head_before_token = head_first ? 1 : 0;
-        e = gqa::launch_stream_bf16(shape, tk, tv, a, plan.num_ctas, stream);
+        gqa::FusedFrontArgs ff;
+        if (front != nullptr) {
+            ff.k_new = front->k_new;
+            ff.v_new = front->v_new;
+            ff.qk_weight = front->qk_weight;
+            ff.q_out = front->q_out;
+            ff.sin_cache = front->sin_cache;
+            ff.cos_cache = front->cos_cache;
+            ff.table_len = front->table_len;
+            ff.eps = front->eps;
+        }
+        e = gqa::launch_stream_bf16(tk, tv, a, front != nullptr ? &ff : nullptr, plan.num_ctas,
+                                    stream);
     } else {
         e = gqa::launch_stream_f32(a, plan.num_ctas, stream);
     }
     if (e != cudaSuccess) return GQA_ERR_CUDA;
     if (plan.needs_combine) {
-        const bool fuse = sequence_parallel || (gather != nullptr && gqa::combine_can_gather(
-                                                    p->batch, p->num_q_heads, sms));
-        e = gqa::launch_combine(a, p->dtype == GQA_DTYPE_BF16, stream, fuse ? gather : nullptr,
-                                sequence_parallel);
+        gqa::CombineKind kind = gqa::CombineKind::kLocal;
+        gqa::PeerGatherArgs to_records;
+        if (mode == DecodeMode::kSeqPar) {
+            kind = gqa::CombineKind::kSeqPar;
+        } else if (mode == DecodeMode::kRecords) {
+            kind = gqa::CombineKind::kRecord;
+            std::memset(&to_records, 0, sizeof(to_records));
+            to_records.recv = reinterpret_cast<uint32_t*>(records);
+            gather = &to_records;
+        } else if (gather != nullptr && gqa::combine_can_gather(rows, sms)) {
+            kind = gqa::CombineKind::kGather;
+        }
+        e = gqa::launch_combine(a, p->dtype == GQA_DTYPE_BF16, stream,
+                                kind == gqa::CombineKind::kLocal ? nullptr : gather, kind);
         if (e != cudaSuccess) return GQA_ERR_CUDA;
-        if (fused != nullptr) *fused = fuse;
+        if (fused != nullptr) *fused = kind == gqa::CombineKind::kGather;
     }
     return GQA_OK;
 }
@@ -594,7 +723,9 @@ extern "C" {
 
 int gqa_qk_norm_rope_append(const gqa_front_params* p) {
     if (p == nullptr) return GQA_ERR_NULL;
-    if (p->batch <= 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0) return GQA_ERR_SHAPE;
+    if (p->batch <= 0 || p->num_q_heads <= 0 || p->num_kv_heads <= 0 || p->q_tokens < 0) {
+        return GQA_ERR_SHAPE;
+    }
     if (p->head_dim != kHeadDim) return GQA_ERR_SHAPE;
     int rc = validate_layout(p->layout, GQA_DTYPE_BF16, p->num_kv_heads);
     if (rc != GQA_OK) return rc;
@@ -622,12 +753,14 @@ int gqa_qk_norm_rope_append(const gqa_front_params* p) {
         if (p->fixed_block < 0 || p->fixed_block >= p->layout.num_blocks) return GQA_ERR_RANGE;
         capacity = p->layout.block_tokens;
     }
+    const int32_t tokens = p->q_tokens > 0 ? p->q_tokens : 1;
+    if (k_in_place && tokens != 1) return GQA_ERR_UNSUPPORTED;
     int32_t uniform_pos = 0;
     if (p->positions_host != nullptr) {
         for (int32_t b = 0; b < p->batch; ++b) {
-            const int32_t pos = p->positions_host[b];
-            if (pos < 0 || pos >= capacity) return GQA_ERR_RANGE;
-            if (p->sin_cache != nullptr && pos >= p->table_len) return GQA_ERR_RANGE;
+            const int32_t pos = p->positions_host[b];  // of the first new token
+            if (pos < 0 || (int64_t)pos + tokens > capacity) return GQA_ERR_RANGE;
+            if (p->sin_cache != nullptr && pos + tokens > p->table_len) return GQA_ERR_RANGE;
             if (p->positions_dev == nullptr && pos != p->positions_host[0]) {
                 return GQA_ERR_UNSUPPORTED;
             }
@@ -636,6 +769,11 @@ int gqa_qk_norm_rope_append(const gqa_front_params* p) {
     }
     gqa::FrontArgs f;
     std::memset(&f, 0, sizeof(f));
+    f.q_tokens = tokens;
+    f.pos_capacity = (int32_t)(capacity > INT32_MAX ? INT32_MAX : capacity);
+    f.table_len = p->table_len;
+    f.num_blocks = p->layout.num_blocks;
+    f.status = p->status_dev;
     f.q = p->q;
     f.q_out = p->q_out;
     f.k_new = p->k_new;

@@ -119,6 +119,10 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// A running maximum as the reference point of 2^(x - m): -inf (nothing seen yet) reads as 0,
+// so that an empty set of keys stays at (m = -inf, l = 0, O = 0) instead of turning into NaN.
+__device__ __forceinline__ float safe_max(float m) { return m == -INFINITY ? 0.0f : m; }
+
 // Packs two floats to BF16 (round to nearest even); `lo` lands in bits 0-15.
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     uint32_t r;
@@ -143,39 +147,5 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 __device__ __forceinline__ void pdl_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
-
-// Optional device-side timeline for tuning builds (-DGQA_TIMELINE): every mark keeps the
-// earliest and the latest %globaltimer value seen at that point of a launch, in one of four
-// banks chosen by `call` (the block index of the launch, so that consecutive layers of a
-// captured graph can be told apart). Compiles to nothing otherwise.
-#ifdef GQA_TIMELINE
-extern __device__ unsigned long long g_timeline[64];
-extern __device__ unsigned long long g_cta_marks[4 * 1024];  // per CTA: smid, first data, merge, end
-__device__ __forceinline__ void timeline_cta(int field) {
-    if (threadIdx.x == 0 && blockIdx.x < 1024) {
-        unsigned long long t;
-        if (field == 0) {
-            unsigned int smid;
-            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-            t = smid;
-        } else {
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        }
-        g_cta_marks[4 * blockIdx.x + field] = t;
-    }
-}
-__device__ __forceinline__ void timeline_mark(int slot, int call) {
-    slot += 8 * (call & 3);
-    if ((threadIdx.x & 31) == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        atomicMin(&g_timeline[2 * slot], t);
-        atomicMax(&g_timeline[2 * slot + 1], t);
-    }
-}
-#else
-__device__ __forceinline__ void timeline_mark(int, int) {}
-__device__ __forceinline__ void timeline_cta(int) {}
-#endif
 
 }  // namespace gqa

@@ -5,9 +5,16 @@
 // bus directly (it writes the rotated query to device memory, where the attention kernel reads
 // it many times), and the attention (or the gather) writes its output straight into a second
 // pinned block. The step then waits for the stream and hands the output to the caller.
-// GQA_SESSION_COPIES=1 in the environment selects explicit cudaMemcpyAsync staging instead.
+// GQA_SESSION_COPIES=1 in the environment selects explicit cudaMemcpyAsync staging instead;
+// GQA_SESSION_FUSED=1 runs the front stage inside the attention kernel (gqa_decode_fused).
+//
+// On a KV-head-parallel node the attention's combine kernel pushes the finished rows to the
+// other ranks and writes the gathered rows straight into the pinned output block, so a step
+// is front stage + attention + combine there too. Which gather runs is decided from the
+// communicator's state and the sizes, which are the same on every rank.
 #include "../../include/gqa_b200.h"
 
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
 #include <new>
@@ -35,7 +42,12 @@ struct gqa_session {
     size_t workspace_bytes;
     float* sin_table;  // [max_seq_len, head_dim / 2], built once at creation
     float* cos_table;
+    int32_t* status;   // pinned, device-mapped status word of the step's kernels
+    cudaEvent_t done;  // recorded behind the step's last launch
     bool zero_copy;    // kernels read / write the pinned blocks directly
+    bool fused_front;  // the attention kernel runs the front stage itself
+    bool spin_wait;    // wait for a step by polling the event, not by blocking in the driver
+    int64_t timing_ns[4];  // last step: staging, launches, wait, copy-out
 };
 
 namespace {
@@ -59,6 +71,8 @@ void release(gqa_session* s) {
     if (s->workspace) cudaFree(s->workspace);
     if (s->sin_table) cudaFree(s->sin_table);
     if (s->cos_table) cudaFree(s->cos_table);
+    if (s->status) cudaFreeHost(s->status);
+    if (s->done) cudaEventDestroy(s->done);
     if (s->stream) cudaStreamDestroy(s->stream);
     delete s;
 }
@@ -87,6 +101,10 @@ int gqa_session_create(int32_t dtype, int32_t max_batch, int32_t num_q_heads,
     s->max_seq_len = max_seq_len;
     const char* copies = std::getenv("GQA_SESSION_COPIES");
     s->zero_copy = !(copies != nullptr && copies[0] == '1');
+    const char* fused = std::getenv("GQA_SESSION_FUSED");
+    s->fused_front = fused != nullptr && fused[0] == '1';
+    const char* wait = std::getenv("GQA_SESSION_WAIT");
+    s->spin_wait = !(wait != nullptr && wait[0] == 's');  // "sync": cudaStreamSynchronize
     s->in_bytes = q_bytes(s, max_batch) + 2 * kv_bytes(s, max_batch) + 2 * (size_t)max_batch * 4;
     int sms = 0, dev = 0;
     bool ok = cudaGetDevice(&dev) == cudaSuccess &&
@@ -97,6 +115,9 @@ int gqa_session_create(int32_t dtype, int32_t max_batch, int32_t num_q_heads,
     s->workspace_bytes = ((size_t)16 * (sms > 0 ? sms : 1) +
                           (size_t)2 * max_batch * num_kv_heads) * rec;
     ok = ok && cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&s->done, cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaMallocHost(&s->status, sizeof(int32_t)) == cudaSuccess;
+    if (ok) *s->status = 0;
     ok = ok && cudaMallocHost(&s->host_in, s->in_bytes) == cudaSuccess;
     ok = ok && cudaMallocHost(&s->host_out, q_bytes(s, max_batch)) == cudaSuccess;
     ok = ok && cudaMalloc(&s->dev_in, s->in_bytes) == cudaSuccess;
@@ -118,6 +139,43 @@ int gqa_session_create(int32_t dtype, int32_t max_batch, int32_t num_q_heads,
 
 void gqa_session_destroy(gqa_session* s) { release(s); }
 
+namespace {
+
+using Clock = std::chrono::steady_clock;
+
+int64_t ns_between(Clock::time_point a, Clock::time_point b) {
+    return std::chrono::duration_cast<std::chrono::nanoseconds>(b - a).count();
+}
+
+// Waits for everything launched on the session's stream. Polling the event keeps the wake-up
+// latency of a blocking wait (tens of microseconds when the host is busy) out of the step; the
+// poll gives up after ten seconds and falls back to the blocking call.
+int wait_for_step(gqa_session* s) {
+    if (!s->spin_wait) {
+        return cudaStreamSynchronize(s->stream) == cudaSuccess ? GQA_OK : GQA_ERR_CUDA;
+    }
+    if (cudaEventRecord(s->done, s->stream) != cudaSuccess) return GQA_ERR_CUDA;
+    const Clock::time_point start = Clock::now();
+    for (uint32_t spins = 1;; ++spins) {
+        const cudaError_t e = cudaEventQuery(s->done);
+        if (e == cudaSuccess) return GQA_OK;
+        if (e != cudaErrorNotReady) return GQA_ERR_CUDA;
+        if ((spins & 1023u) == 0 && ns_between(start, Clock::now()) > 10000000000ll) {
+            return cudaStreamSynchronize(s->stream) == cudaSuccess ? GQA_OK : GQA_ERR_CUDA;
+        }
+    }
+}
+
+// What the kernels left in the status word, as a return code.
+int status_code(gqa_session* s) {
+    const int32_t st = *reinterpret_cast<volatile int32_t*>(s->status);
+    if (st == 0) return GQA_OK;
+    *s->status = 0;
+    return st == GQA_STATUS_BAD_INPUT ? GQA_ERR_RANGE : GQA_ERR_TIMEOUT;
+}
+
+}  // namespace
+
 static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* q_host,
                      const void* k_host, const void* v_host, const void* qk_weight_dev,
                      void* k_cache, void* v_cache, const gqa_kv_layout* layout,
@@ -129,6 +187,7 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
         return GQA_ERR_NULL;
     }
     if (batch <= 0 || batch > s->max_batch) return GQA_ERR_SHAPE;
+    const Clock::time_point t_start = Clock::now();
     const size_t qb = q_bytes(s, batch), kb = kv_bytes(s, batch);
     // Offsets follow the max_batch layout so device pointers stay 16-byte aligned.
     const size_t off_k = q_bytes(s, s->max_batch);
@@ -141,7 +200,7 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     int32_t* lens = reinterpret_cast<int32_t*>(s->host_in + off_len);
     int32_t* poss = reinterpret_cast<int32_t*>(s->host_in + off_pos);
     for (int32_t b = 0; b < batch; ++b) {
-        if (positions_host[b] < 0) return GQA_ERR_RANGE;
+        if (positions_host[b] < 0 || positions_host[b] >= s->max_seq_len) return GQA_ERR_RANGE;
         poss[b] = positions_host[b];
         lens[b] = positions_host[b] + 1;
     }
@@ -155,34 +214,49 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     }
     bool uniform = true;
     for (int32_t b = 1; b < batch; ++b) uniform = uniform && positions_host[b] == positions_host[0];
+    const Clock::time_point t_staged = Clock::now();
 
-    gqa_front_params f;
-    std::memset(&f, 0, sizeof(f));
-    f.batch = batch;
-    f.num_q_heads = s->num_q_heads;
-    f.num_kv_heads = s->num_kv_heads;
-    f.head_dim = s->head_dim;
-    f.blocks_per_seq = blocks_per_seq;
-    f.fixed_block = fixed_block;
-    f.eps = 1e-6f;
-    f.layout = *layout;
-    f.q = in;
-    f.q_out = s->dev_in;
-    f.k_new = in + off_k;
-    f.v_new = in + off_v;
-    f.qk_weight = qk_weight_dev;
-    f.sin_cache = s->sin_table;
-    f.cos_cache = s->cos_table;
-    f.table_len = s->max_seq_len;
-    f.k_cache = k_cache;
-    f.v_cache = v_cache;
-    f.positions_host = poss;
-    // Equal positions travel by value; otherwise the kernels read them from the staged block.
-    f.positions_dev = uniform ? nullptr : reinterpret_cast<const int32_t*>(in + off_pos);
-    f.block_table_dev = block_table_dev;
-    f.stream = s->stream;
-    int rc = gqa_qk_norm_rope_append(&f);
-    if (rc != GQA_OK) return rc;
+    int rc = GQA_OK;
+    gqa_fused_front ff;
+    std::memset(&ff, 0, sizeof(ff));
+    if (s->fused_front) {
+        ff.k_new = in + off_k;
+        ff.v_new = in + off_v;
+        ff.qk_weight = qk_weight_dev;
+        ff.sin_cache = s->sin_table;
+        ff.cos_cache = s->cos_table;
+        ff.table_len = s->max_seq_len;
+        ff.eps = 1e-6f;
+    } else {
+        gqa_front_params f;
+        std::memset(&f, 0, sizeof(f));
+        f.batch = batch;
+        f.num_q_heads = s->num_q_heads;
+        f.num_kv_heads = s->num_kv_heads;
+        f.head_dim = s->head_dim;
+        f.blocks_per_seq = blocks_per_seq;
+        f.fixed_block = fixed_block;
+        f.eps = 1e-6f;
+        f.layout = *layout;
+        f.q = in;
+        f.q_out = s->dev_in;
+        f.k_new = in + off_k;
+        f.v_new = in + off_v;
+        f.qk_weight = qk_weight_dev;
+        f.sin_cache = s->sin_table;
+        f.cos_cache = s->cos_table;
+        f.table_len = s->max_seq_len;
+        f.k_cache = k_cache;
+        f.v_cache = v_cache;
+        f.positions_host = poss;
+        // Equal positions travel by value; otherwise the kernels read them from the staged block.
+        f.positions_dev = uniform ? nullptr : reinterpret_cast<const int32_t*>(in + off_pos);
+        f.block_table_dev = block_table_dev;
+        f.status_dev = s->status;
+        f.stream = s->stream;
+        rc = gqa_qk_norm_rope_append(&f);
+        if (rc != GQA_OK) return rc;
+    }
 
     gqa_decode_params p;
     std::memset(&p, 0, sizeof(p));
@@ -194,7 +268,7 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     p.blocks_per_seq = blocks_per_seq;
     p.fixed_block = fixed_block;
     p.layout = *layout;
-    p.q = s->dev_in;
+    p.q = s->fused_front ? static_cast<const void*>(in) : s->dev_in;
     p.k_cache = k_cache;
     p.v_cache = v_cache;
     const bool out_to_host = s->zero_copy && comm == nullptr;
@@ -204,12 +278,12 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     p.seq_lens_host = lens;
     p.seq_lens_dev = uniform ? nullptr : reinterpret_cast<const int32_t*>(in + off_len);
     p.block_table_dev = block_table_dev;
+    p.status_dev = s->status;
     p.stream = s->stream;
     // Ahead of the attention in this stream is the front stage, which writes the cache rows
-    // of the new positions only.
+    // of the new positions only (fused: nothing that writes the caches at all).
     p.early_prefetch = 1;
-    rc = gqa_decode(&p);
-    if (rc != GQA_OK) return rc;
+    const gqa_fused_front* front = s->fused_front ? &ff : nullptr;
 
     if (comm != nullptr) {
         const int32_t nranks = gqa_comm_nranks(comm);
@@ -227,31 +301,54 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
             }
             s->gather_bytes = cap;
         }
-        // The peer-store gather can deliver into the pinned block itself; NCCL gathers on the
-        // device and a copy follows.
-        bool on_host = false;
-        if (s->zero_copy) {
-            rc = gqa_comm_peer_gather(comm, s->dev_out, s->host_gather, qb, nullptr, s->stream);
-            on_host = rc == GQA_OK;
+        // The peer-store gather (inside the combine kernel when units are split) can deliver
+        // into the pinned block itself; NCCL gathers on the device and a copy follows. The
+        // choice depends on the communicator and the size only, so every rank makes the same.
+        const bool to_host = s->zero_copy && gqa_comm_peer_gather_fits(comm, qb) == 1;
+        rc = gqa_decode_sharded_fused(&p, front, comm, to_host ? s->host_gather : s->dev_gather);
+        if (rc != GQA_OK) return rc;
+        if (!to_host && cudaMemcpyAsync(s->host_gather, s->dev_gather, total,
+                                        cudaMemcpyDeviceToHost, s->stream) != cudaSuccess) {
+            return GQA_ERR_CUDA;
         }
-        if (!on_host) {
-            rc = gqa_comm_all_gather(comm, s->dev_out, s->dev_gather, qb, s->stream);
-            if (rc != GQA_OK) return rc;
-            if (cudaMemcpyAsync(s->host_gather, s->dev_gather, total, cudaMemcpyDeviceToHost,
-                                s->stream) != cudaSuccess) {
-                return GQA_ERR_CUDA;
-            }
-        }
-        if (cudaStreamSynchronize(s->stream) != cudaSuccess) return GQA_ERR_CUDA;
+        const Clock::time_point t_launched = Clock::now();
+        rc = wait_for_step(s);
+        if (rc != GQA_OK) return rc;
+        const Clock::time_point t_done = Clock::now();
+        rc = status_code(s);
+        if (rc != GQA_OK) return rc;
         std::memcpy(out_host, s->host_gather, total);
+        const Clock::time_point t_end = Clock::now();
+        s->timing_ns[0] = ns_between(t_start, t_staged);
+        s->timing_ns[1] = ns_between(t_staged, t_launched);
+        s->timing_ns[2] = ns_between(t_launched, t_done);
+        s->timing_ns[3] = ns_between(t_done, t_end);
         return GQA_OK;
     }
+    rc = front != nullptr ? gqa_decode_fused(&p, front) : gqa_decode(&p);
+    if (rc != GQA_OK) return rc;
     if (!out_to_host && cudaMemcpyAsync(s->host_out, s->dev_out, qb, cudaMemcpyDeviceToHost,
                                         s->stream) != cudaSuccess) {
         return GQA_ERR_CUDA;
     }
-    if (cudaStreamSynchronize(s->stream) != cudaSuccess) return GQA_ERR_CUDA;
+    const Clock::time_point t_launched = Clock::now();
+    rc = wait_for_step(s);
+    if (rc != GQA_OK) return rc;
+    const Clock::time_point t_done = Clock::now();
+    rc = status_code(s);
+    if (rc != GQA_OK) return rc;
     std::memcpy(out_host, s->host_out, qb);
+    const Clock::time_point t_end = Clock::now();
+    s->timing_ns[0] = ns_between(t_start, t_staged);
+    s->timing_ns[1] = ns_between(t_staged, t_launched);
+    s->timing_ns[2] = ns_between(t_launched, t_done);
+    s->timing_ns[3] = ns_between(t_done, t_end);
+    return GQA_OK;
+}
+
+int gqa_session_last_timing(const gqa_session* s, int64_t* ns_out) {
+    if (s == nullptr || ns_out == nullptr) return GQA_ERR_NULL;
+    for (int i = 0; i < 4; ++i) ns_out[i] = s->timing_ns[i];
     return GQA_OK;
 }
 

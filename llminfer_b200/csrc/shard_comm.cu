@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(kGatherThreads) peer_gather_kernel(const PeerG
     if (threadIdx.x == 0) {
         if (s_timed_out) {
             ctrl->status = 1;
-            if (a.status != nullptr) atomicExch(a.status, 2);
+            if (a.status != nullptr) atomicExch(a.status, gqa::kStatusPeerTimeout);
         }
         // The last CTA to finish advances the step counter for the next launch.
         __threadfence();
@@ -306,6 +306,12 @@ int gqa_comm_peer_gather(gqa_comm* comm, const void* send, void* recv, size_t by
     return e == cudaSuccess ? GQA_OK : GQA_ERR_CUDA;
 }
 
+int gqa_comm_peer_gather_fits(const gqa_comm* comm, size_t bytes) {
+    if (comm == nullptr) return 0;
+    return comm->window_local != nullptr && bytes != 0 && bytes % 16 == 0 &&
+                   2 * bytes <= comm->slot_bytes ? 1 : 0;
+}
+
 void gqa_comm_disable_peer_gather(gqa_comm* comm) {
     if (comm == nullptr || comm->window_local == nullptr) return;
     cudaDeviceSynchronize();
@@ -339,11 +345,17 @@ int gqa_comm_all_gather(gqa_comm* comm, const void* send, void* recv, size_t byt
     return GQA_OK;
 }
 
-int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathered) {
+int gqa_decode_sharded_fused(const gqa_decode_params* p, const gqa_fused_front* front,
+                             gqa_comm* comm, void* gathered) {
     if (p == nullptr || comm == nullptr || gathered == nullptr) return GQA_ERR_NULL;
-    if (p->batch <= 0 || p->num_q_heads <= 0 || p->head_dim <= 0) return GQA_ERR_SHAPE;
+    if (p->batch <= 0 || p->num_q_heads <= 0 || p->head_dim <= 0 || p->q_tokens < 0) {
+        return GQA_ERR_SHAPE;
+    }
     const size_t elem = p->dtype == GQA_DTYPE_F32 ? 4 : 2;
-    const size_t bytes = (size_t)p->batch * p->num_q_heads * p->head_dim * elem;
+    const size_t tokens = p->q_tokens > 0 ? p->q_tokens : 1;
+    const size_t bytes = (size_t)p->batch * tokens * p->num_q_heads * p->head_dim * elem;
+    // Which gather runs depends on the communicator's state and the sizes only, which are the
+    // same on every rank: the ranks cannot end up in different collectives.
     const bool peer = comm->window_local != nullptr && 2 * bytes <= comm->slot_bytes &&
                       bytes % 16 == 0 && p->out != nullptr &&
                       ((reinterpret_cast<uintptr_t>(p->out) |
@@ -352,16 +364,20 @@ int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathere
         // The combine kernel pushes each row to the peers as soon as it is merged.
         const PeerGatherArgs g = gather_args(comm, p->out, gathered, bytes, p->status_dev);
         bool fused = false;
-        const int rc = gqa::decode_with_gather(p, &g, &fused);
+        const int rc = gqa::decode_with_gather(p, front, &g, &fused);
         if (rc != GQA_OK || fused) return rc;
         return gqa_comm_peer_gather(comm, p->out, gathered, bytes, p->status_dev, p->stream);
     }
-    const int rc = gqa_decode(p);
+    const int rc = front != nullptr ? gqa_decode_fused(p, front) : gqa_decode(p);
     if (rc != GQA_OK) return rc;
     if (peer) {
         return gqa_comm_peer_gather(comm, p->out, gathered, bytes, p->status_dev, p->stream);
     }
     return gqa_comm_all_gather(comm, p->out, gathered, bytes, p->stream);
+}
+
+int gqa_decode_sharded(const gqa_decode_params* p, gqa_comm* comm, void* gathered) {
+    return gqa_decode_sharded_fused(p, nullptr, comm, gathered);
 }
 
 int gqa_decode_seqpar(const gqa_decode_params* p, gqa_comm* comm) {

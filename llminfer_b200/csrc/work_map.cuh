@@ -6,8 +6,13 @@
 //   chunk = 32 consecutive keys of a unit;
 //   item  = (unit, split): `split_chunks` consecutive chunks of a unit. Item ids are
 //           sequence-major, then kv head, then split, so the partial record of an item sits
-//           at workspace + item * group * (head_dim + 2) floats: O[group][head_dim] scaled
-//           to the item's own running maximum, then m[group], then l[group].
+//           at workspace + item * cols * (head_dim + 2) floats, cols = q_tokens * group:
+//           O[cols][head_dim] scaled to the item's own running maximum, then m[cols], then
+//           l[cols]. Column c of a unit is query token c / group, query head c % group.
+//
+// Lengths, block ids and record indices that come from device memory are never trusted: a
+// length is clamped to what a sequence can hold, a record that would not fit the caller's
+// scratch is not written, and the status word is raised (kStatusBadInput) instead.
 #pragma once
 
 #include <cstdint>
@@ -17,6 +22,13 @@ namespace gqa {
 constexpr int kChunkKeys = 32;
 constexpr int kHeadDim = 128;
 constexpr int kMaxRaggedBatch = 1024;
+
+// Values of the caller's status word.
+constexpr int kStatusStageTimeout = 1;  // a staged chunk did not arrive within the time limit
+constexpr int kStatusPeerTimeout = 2;   // a peer's words did not arrive within the time limit
+constexpr int kStatusBadInput = 3;      // a device-side length, position or block id was out
+                                        // of range (clamped or skipped), or a record did not
+                                        // fit the scratch
 
 struct DecodeArgs {
     const void* q;
@@ -42,8 +54,19 @@ struct DecodeArgs {
     int32_t head_before_token;  // order of the middle tensor-map coordinates (BF16 path)
     int32_t early_prefetch;     // K/V stages may be requested before the predecessor is done
     int32_t always_partial;     // every item leaves a partial record, even a unit's only one
+    int32_t q_tokens;           // query tokens per sequence (token t attends len - (T-1-t) keys)
+    int32_t q_token_stride;     // tokens per sequence in q / out / k_new (>= q_tokens: a launch
+    int32_t q_token_first;      //   may cover tokens [first, first + q_tokens) of a longer run)
+    int32_t len_offset;         // subtracted from every device length (tokens of later passes)
+    int32_t len_capacity;       // keys a sequence can hold (device lengths are clamped to it)
+    int32_t item_capacity;      // partial records the scratch can hold
+    int32_t num_blocks;         // blocks in the cache (block ids are checked against it)
     float scale_log2;  // (1 / sqrt(head_dim)) * log2(e)
 };
+
+__device__ inline void raise_status(const DecodeArgs& a, int code) {
+    if (a.status != nullptr) atomicExch(a.status, code);
+}
 
 struct Item {
     int32_t b;
@@ -71,7 +94,13 @@ __device__ inline WorkTables build_work_tables(const DecodeArgs& a, int32_t* sme
     int32_t* s_len = smem_ints;
     int32_t* s_base = smem_ints + (a.batch + 1);
     for (int32_t b = threadIdx.x; b < a.batch; b += blockDim.x) {
-        s_len[b] = a.seq_lens_dev[b];
+        // A sequence holds at least its query tokens and at most the cache's capacity; zero
+        // means "no keys here" (an empty slice of a sequence-parallel rank) and yields no item.
+        const int32_t raw = a.seq_lens_dev[b] - a.len_offset;
+        int32_t len = min(max(raw, 0), a.len_capacity);
+        if (len != 0 && len < a.q_tokens) len = 0;
+        if (len != raw && blockIdx.x == 0) raise_status(a, kStatusBadInput);
+        s_len[b] = len;
     }
     __syncthreads();
     if (threadIdx.x < 32) {

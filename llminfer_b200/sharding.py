@@ -40,16 +40,15 @@ def sequence_slice(seq_lens, block_table, block_tokens: int, nranks: int, rank: 
     logical order (nested lists or an array). Returns (local_table, local_lens): the rank's
     block table, padded with zeros to the original width, and the number of keys in its
     blocks. Only the globally last block of a sequence can be partly filled, and it is the
-    last block of the rank that holds it, so a local sequence is an ordinary one. Raises
-    ValueError when a rank would hold no key of some sequence.
+    last block of the rank that holds it, so a local sequence is an ordinary one. A rank that
+    holds no block of a sequence (a sequence shorter than `nranks` blocks) gets length 0 for
+    it: gqa_decode_seqpar and gqa_decode_partial take that as an empty slice.
     """
     local_table, local_lens = [], []
     for length, row in zip(seq_lens, block_table):
         row = [int(v) for v in row]
         blocks = -(-int(length) // block_tokens)
         mine = list(range(rank, blocks, nranks))
-        if not mine:
-            raise ValueError(f"rank {rank} of {nranks} holds no key of a sequence of {length} keys")
         keys = sum(min(block_tokens, int(length) - i * block_tokens) for i in mine)
         local_table.append([row[i] for i in mine] + [0] * (len(row) - len(mine)))
         local_lens.append(keys)

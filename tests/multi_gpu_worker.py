@@ -185,7 +185,7 @@ def main() -> None:
     # Sequence-parallel: every rank holds all heads and every world-th block of each sequence;
     # the combine kernel merges the ranks' records. Every rank gets the same bits, and they
     # agree with the oracle on the whole sequences.
-    sp_lens = [3000, 2100, 2048]
+    sp_lens = [3000, 200, 2048]  # rank 1 and up hold no key of the second sequence
     local_rows, local_lens = sharding.sequence_slice(sp_lens, table, block_tokens, world, rank)
     local_tab = np.array(local_rows, dtype=np.int32)
     layout_sp = gqa.layout_pool(num_blocks, block_tokens, hkv)

@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol(gqa):
     for name in sorted(declared):
         assert hasattr(handle, name), f"{name} is declared in the header but not exported"
     assert declared == set(gqa.binding.exported_symbols())
-    assert handle.gqa_abi_version() == 1
+    assert handle.gqa_abi_version() == 2
     assert gqa.status_string(0) == "ok"
     assert "workspace" in gqa.status_string(-6)
 
@@ -99,7 +99,8 @@ def test_binding_structs_match_the_header_layout(gqa, tmp_path):
     from llminfer_b200 import binding as B
     mirrors = {"gqa_kv_layout": B._Layout, "gqa_decode_params": B._DecodeParams,
                "gqa_decode_plan_info": B._PlanInfo, "gqa_front_params": B._FrontParams,
-               "gqa_oproj_params": B._OprojParams, "gqa_qkv_params": B._QkvParams}
+               "gqa_oproj_params": B._OprojParams, "gqa_qkv_params": B._QkvParams,
+               "gqa_fused_front": B._FusedFront}
     lines = ["#include <stddef.h>", "#include <stdio.h>", '#include "gqa_b200.h"', "int main(void) {"]
     for name, mirror in mirrors.items():
         lines.append(f'printf("{name} %zu\\n", sizeof({name}));')
