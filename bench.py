@@ -433,12 +433,17 @@ class Workload:
     def launches_per_step(self, gather: str) -> int:
         """Kernels of this library per step: (front stage,) streaming kernel, combine; the
         gather is one more launch unless the combine kernel carries it."""
-        n = 1 + (1 if self.plan["needs_combine"] else 0)
+        n = 1 + (1 if self.plan["needs_combine"] and not self.cluster_merge() else 0)
         if self.has_front and not self.fused_front:
             n += 1
         if self.world > 1 and not self.seq_parallel and not self.fused_gather(gather):
             n += 1
         return n
+
+    def cluster_merge(self) -> bool:
+        """Splits merged inside thread-block clusters by the streaming kernel: no combine launch."""
+        return (self.comm is None and self.plan.get("cluster_size", 0) > 0
+                and os.environ.get("GQA_CLUSTER_MERGE", "1")[:1] != "0")
 
     def fused_gather(self, gather: str) -> bool:
         return (self.world > 1 and gather == "peer" and bool(self.plan["needs_combine"])
@@ -787,7 +792,8 @@ def sweep_row(gqa, torch, name, timer, args, dev) -> dict:
     row.update(attention_only_us_per_layer=attn["median_us"], attention_only_min_us=attn["min_us"],
                gbs=gbs, frac_of_measured_peak=gbs / peak, frac_of_8tbs_nominal=gbs / 8000.0,
                algorithmic_bytes=w.bytes_per_step(), split_chunks=w.plan["split_chunks"],
-               ctas=w.plan["num_ctas"], layers_cycled=w.slots,
+               ctas=w.plan["num_ctas"], cluster_size=w.plan.get("cluster_size", 0) if w.cluster_merge() else 0,
+               layers_cycled=w.slots,
                launches_per_step=w.launches_per_step("peer"))
     if w.has_front:
         w.attention(0)

@@ -170,7 +170,10 @@ typedef struct gqa_decode_plan_info {
     int32_t num_items;        /* (sequence, kv head, split) work items (upper bound) */
     int32_t num_ctas;         /* grid of the streaming kernel */
     int32_t needs_combine;    /* 1 when a second, LSE-combine launch follows */
-    int32_t reserved;
+    int32_t cluster_size;     /* > 0: gqa_decode can merge the splits inside thread-block clusters
+                                 of this many CTAs (one cluster per (sequence, kv head), one CTA
+                                 per split) instead: no combine launch and no workspace, provided
+                                 the GPU holds all clusters at once and no gather is fused in */
     size_t workspace_bytes;   /* scratch the chosen plan needs */
 } gqa_decode_plan_info;
 
@@ -510,6 +513,11 @@ int gqa_decode_seqpar(const gqa_decode_params* p, gqa_comm* comm);
  * 4 * local_kv_heads * min(batch, 8) * hidden). Every rank ends with the same, complete
  * `residual`, bit-equal to what the unsharded call computes. A wait that runs out sets
  * *status_dev to 2.
+ *
+ * The CTAs of a launch hand their partial sums to one another, so the grid is sized to be
+ * resident all at once on an otherwise idle GPU: run the call on a stream that has the GPU to
+ * itself (kernels of other streams that hold SMs at the same time can delay CTAs past the
+ * two-second limit of those waits, which then report GQA_STATUS_PEER_TIMEOUT).
  */
 typedef struct gqa_oproj_params {
     int32_t batch;        /* tokens (sequences of a decode step) */

@@ -73,7 +73,7 @@ class _PlanInfo(C.Structure):
         ("num_items", C.c_int32),
         ("num_ctas", C.c_int32),
         ("needs_combine", C.c_int32),
-        ("reserved", C.c_int32),
+        ("cluster_size", C.c_int32),
         ("workspace_bytes", C.c_size_t),
     ]
 
@@ -358,7 +358,7 @@ def decode_plan(*, dtype: int, batch: int, num_q_heads: int, num_kv_heads: int, 
     p.block_table_dev = fake if paged else None
     info = _PlanInfo()
     _check(lib().gqa_decode_plan(C.byref(p), sm_count, C.byref(info)), "gqa_decode_plan")
-    return {f: getattr(info, f) for f, _ in _PlanInfo._fields_ if f != "reserved"}
+    return {f: getattr(info, f) for f, _ in _PlanInfo._fields_}
 
 
 def decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, *,

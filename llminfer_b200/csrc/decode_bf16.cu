@@ -38,6 +38,14 @@
 // value row, patches both into the staged tile in shared memory and appends them to the cache
 // in HBM. Nothing else in the launch reads those cache rows, so no ordering between CTAs is
 // needed.
+//
+// CLUSTER launches one thread-block cluster per unit with one CTA per split (at most 8): each
+// CTA streams its split, leaves its (O, m, l) in its own shared memory, and after a cluster
+// barrier the CTAs of the cluster merge the splits by reading one another's shared memory
+// (distributed shared memory) and write the final rows. Short contexts, where the whole launch
+// is one wave of CTAs and a second launch costs as much as the streaming, then need no combine
+// kernel and no trip through the scratch. The merge performs the combine kernel's operations in
+// the combine kernel's order, so both paths give the same bits.
 #include <mutex>
 
 #include "decode_kernels.cuh"
@@ -86,7 +94,7 @@ struct Cursor {
 
 }  // namespace
 
-template <int WARPS, int STAGES, int KEYS, int OCC, int NT, bool FUSED>
+template <int WARPS, int STAGES, int KEYS, int OCC, int NT, bool FUSED, bool CLUSTER>
 __global__ void __launch_bounds__(WARPS * 32, OCC)
 gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const DecodeArgs a,
@@ -106,7 +114,8 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     float* s_l = s_m + WARPS * kCols;
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_l + WARPS * kCols);
     __nv_bfloat16* s_q = reinterpret_cast<__nv_bfloat16*>(s_bar + WARPS * STAGES);
-    int32_t* s_tables = reinterpret_cast<int32_t*>(s_q + (FUSED ? kCols * kQPitch : 0));
+    float* s_rec = reinterpret_cast<float*>(s_q + (FUSED ? kCols * kQPitch : 0));
+    int32_t* s_tables = reinterpret_cast<int32_t*>(s_rec + (CLUSTER ? kCols * (kHeadDim + 2) : 0));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -130,7 +139,15 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     const WorkTables tables = build_work_tables(a, s_tables);
     __syncthreads();
 
-    const int32_t n_items = total_items(a, tables);
+    // Persistent grid: items blockIdx.x, blockIdx.x + gridDim.x, ... Cluster launch: the one
+    // item this CTA's place in its cluster stands for (or none).
+    Item own = {};
+    const bool has_own = CLUSTER ? cluster_item(a, tables, &own) : false;
+    const int32_t n_items = CLUSTER ? (has_own ? (int32_t)blockIdx.x + 1 : 0) : total_items(a, tables);
+    auto item_of = [&](int32_t idx) -> Item {
+        if (CLUSTER) return own;
+        return decode_item(a, tables, idx);
+    };
     const int32_t group = a.group;
     const int32_t q_tokens = a.q_tokens;
     const int32_t cols = group * q_tokens;
@@ -153,7 +170,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
             if (c.item >= n_items) {
                 c.valid = false;
             } else {
-                const Item it = decode_item(a, tables, c.item);
+                const Item it = item_of(c.item);
                 c.b = it.b;
                 c.hk = it.hk;
                 c.k = it.chunk_begin * kChunkKeys / KEYS + warp;
@@ -221,7 +238,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
 
 #pragma unroll 1
     for (int32_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const Item it = decode_item(a, tables, item);
+        const Item it = item_of(item);
         const int32_t new_lo = it.len - q_tokens;  // position of the first query token
 
         // Row of column c in q / out: [sequence][token][query head][channel].
@@ -539,9 +556,9 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
             const bool final_out = (it.nsplits == 1) && a.always_partial == 0;
             // A record that does not fit the scratch is not written (lengths read from the
             // device may have outgrown what the scratch was sized for).
-            const bool fits = final_out || item < a.item_capacity;
+            const bool fits = CLUSTER || final_out || item < a.item_capacity;
             if (!fits && threadIdx.x == 0) raise_status(a, kStatusBadInput);
-            float* rec = a.workspace + (int64_t)item * cols * (kHeadDim + 2);
+            float* rec = CLUSTER ? s_rec : a.workspace + (int64_t)item * cols * (kHeadDim + 2);
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
             for (int idx = threadIdx.x; fits && idx < cols * kHeadDim; idx += WARPS * 32) {
                 const int n = idx >> 7;
@@ -570,10 +587,63 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
         }
         __syncthreads();
     }
+
+    if (CLUSTER) {
+        // Every CTA of the cluster gets here, with or without an item. After the barrier the
+        // records of the unit's splits are readable in their CTAs' shared memory; the rows are
+        // dealt to all threads of the cluster. The arithmetic is gqa_decode_combine's for a
+        // unit of up to 8 splits: weights relative to the largest maximum, products rounded
+        // before they are added, splits in ascending order.
+        cluster_sync_all();
+        const int32_t csize = a.cluster_size;
+        if (own.nsplits > 1) {
+            const int32_t rank = own.split;
+            const uint32_t rec_base = smem_u32(s_rec);
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
+            for (int idx = rank * (WARPS * 32) + threadIdx.x; idx < cols * kHeadDim;
+                 idx += csize * (WARPS * 32)) {
+                const int n = idx >> 7;
+                const int d = idx & (kHeadDim - 1);
+                float ms[8], ls[8], os[8];
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp) {
+                    if (sp < own.nsplits) {
+                        const uint32_t base = cluster_map(rec_base, (uint32_t)sp);
+                        ms[sp] = ld_cluster_f32(base + (cols * kHeadDim + n) * 4);
+                        ls[sp] = ld_cluster_f32(base + (cols * kHeadDim + cols + n) * 4);
+                        os[sp] = ld_cluster_f32(base + idx * 4);
+                    } else {
+                        ms[sp] = -INFINITY; ls[sp] = 0.0f; os[sp] = 0.0f;
+                    }
+                }
+                float tmax = ms[0];
+#pragma unroll
+                for (int sp = 1; sp < 8; ++sp) tmax = fmaxf(tmax, ms[sp]);
+                const float ref = safe_max(tmax);
+                float ltile = 0.0f, acc = 0.0f;
+#pragma unroll
+                for (int sp = 0; sp < 8; ++sp) {
+                    if (sp < own.nsplits) {
+                        const float wgt = ex2_approx(ms[sp] - ref);
+                        ltile = __fmaf_rn(ls[sp], wgt, ltile);
+                        const float part = __fmaf_rn(os[sp], wgt, 0.0f);
+                        acc = sp == 0 ? part : __fadd_rn(acc, part);
+                    }
+                }
+                const int t = n / group;
+                const int64_t row = (((int64_t)own.b * a.q_token_stride + a.q_token_first + t) *
+                                         a.num_q_heads + (int64_t)own.hk * group + (n - t * group)) *
+                                    kHeadDim;
+                out[row + d] = __float2bfloat16(acc / ltile);
+            }
+        }
+        // No CTA may leave (and give up its shared memory) while another still reads it.
+        cluster_sync_all();
+    }
 }
 
 size_t stream_bf16_smem_bytes(int warps, int stages, int keys, int n_tiles, bool fused,
-                              int batch_for_tables) {
+                              bool cluster, int batch_for_tables) {
     const size_t cols = 8 * (size_t)n_tiles;
     size_t bytes = 1024;  // alignment slack
     bytes += (size_t)warps * stages * keys * 512;
@@ -581,17 +651,18 @@ size_t stream_bf16_smem_bytes(int warps, int stages, int keys, int n_tiles, bool
     bytes += 2 * (size_t)warps * cols * sizeof(float);
     bytes += (size_t)warps * stages * sizeof(uint64_t);
     if (fused) bytes += cols * kQPitch * sizeof(__nv_bfloat16);
+    if (cluster) bytes += cols * (kHeadDim + 2) * sizeof(float);
     bytes += 2 * ((size_t)batch_for_tables + 1) * sizeof(int32_t);
     return bytes;
 }
 
-template <int WARPS, int STAGES, int KEYS, int OCC, int NT, bool FUSED>
+template <int WARPS, int STAGES, int KEYS, int OCC, int NT, bool FUSED, bool CLUSTER>
 static cudaError_t launch_variant(const CUtensorMap& tk, const CUtensorMap& tv,
                                   const DecodeArgs& args, const FusedFrontArgs& ff, int grid,
-                                  cudaStream_t stream) {
+                                  cudaStream_t stream, int* max_clusters) {
     const int tables = args.seq_lens_dev != nullptr ? args.batch : 0;
-    const size_t smem = stream_bf16_smem_bytes(WARPS, STAGES, KEYS, NT, FUSED, tables);
-    auto kernel = gqa_decode_stream_bf16<WARPS, STAGES, KEYS, OCC, NT, FUSED>;
+    const size_t smem = stream_bf16_smem_bytes(WARPS, STAGES, KEYS, NT, FUSED, CLUSTER, tables);
+    auto kernel = gqa_decode_stream_bf16<WARPS, STAGES, KEYS, OCC, NT, FUSED, CLUSTER>;
     // The attribute is per function and per device.
     static std::mutex mu;
     static size_t configured[64] = {};
@@ -606,26 +677,72 @@ static cudaError_t launch_variant(const CUtensorMap& tk, const CUtensorMap& tv,
             if (dev >= 0 && dev < 64) configured[dev] = smem;
         }
     }
-    return launch_pdl(kernel, dim3(grid), dim3(WARPS * 32), smem, stream, tk, tv, args, ff);
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    if (CLUSTER) {
+        attrs[1].id = cudaLaunchAttributeClusterDimension;
+        attrs[1].val.clusterDim.x = (unsigned)args.cluster_size;
+        attrs[1].val.clusterDim.y = 1;
+        attrs[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+        if (max_clusters != nullptr) {
+            // Query only: how many clusters of this size the GPU holds at once.
+            *max_clusters = 0;
+            return cudaOccupancyMaxActiveClusters(max_clusters, kernel, &cfg);
+        }
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, tk, tv, args, ff);
 }
 
-cudaError_t launch_stream_bf16(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeArgs& args,
-                               const FusedFrontArgs* fused, int grid, cudaStream_t stream) {
+template <bool CLUSTER>
+static cudaError_t launch_by_shape(const CUtensorMap& tk, const CUtensorMap& tv,
+                                   const DecodeArgs& args, const FusedFrontArgs* fused, int grid,
+                                   cudaStream_t stream, int* max_clusters) {
     constexpr StreamShape S = kDefaultStreamShape;
     FusedFrontArgs ff = {};
     if (fused != nullptr) ff = *fused;
     const int cols = args.group * args.q_tokens;
     if (cols <= 8) {
         return fused != nullptr
-                   ? launch_variant<S.warps, S.stages, S.keys, 1, 1, true>(tk, tv, args, ff, grid, stream)
-                   : launch_variant<S.warps, S.stages, S.keys, 1, 1, false>(tk, tv, args, ff, grid, stream);
+                   ? launch_variant<S.warps, S.stages, S.keys, 1, 1, true, CLUSTER>(
+                         tk, tv, args, ff, grid, stream, max_clusters)
+                   : launch_variant<S.warps, S.stages, S.keys, 1, 1, false, CLUSTER>(
+                         tk, tv, args, ff, grid, stream, max_clusters);
     }
     if (cols <= 16) {
         return fused != nullptr
-                   ? launch_variant<S.warps, S.stages, S.keys, 1, 2, true>(tk, tv, args, ff, grid, stream)
-                   : launch_variant<S.warps, S.stages, S.keys, 1, 2, false>(tk, tv, args, ff, grid, stream);
+                   ? launch_variant<S.warps, S.stages, S.keys, 1, 2, true, CLUSTER>(
+                         tk, tv, args, ff, grid, stream, max_clusters)
+                   : launch_variant<S.warps, S.stages, S.keys, 1, 2, false, CLUSTER>(
+                         tk, tv, args, ff, grid, stream, max_clusters);
     }
     return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_stream_bf16(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeArgs& args,
+                               const FusedFrontArgs* fused, int grid, cudaStream_t stream) {
+    return args.cluster_size > 0
+               ? launch_by_shape<true>(tk, tv, args, fused, grid, stream, nullptr)
+               : launch_by_shape<false>(tk, tv, args, fused, grid, stream, nullptr);
+}
+
+int stream_bf16_max_clusters(const CUtensorMap& tk, const CUtensorMap& tv, const DecodeArgs& args,
+                             const FusedFrontArgs* fused, int grid) {
+    int clusters = 0;
+    if (args.cluster_size <= 0 ||
+        launch_by_shape<true>(tk, tv, args, fused, grid, nullptr, &clusters) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return clusters;
 }
 
 }  // namespace gqa

@@ -339,7 +339,7 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
             float ltile = 0.f;
             for (int32_t i = 0; i < cnt; ++i) {
                 const float w = BF16_OUT ? ex2_approx(s_m[i] - ref) : exp2f(s_m[i] - ref);
-                ltile += s_l[i] * w;
+                ltile = __fmaf_rn(s_l[i], w, ltile);
             }
 #pragma unroll
             for (int t = 0; t < kOwn; ++t) {
@@ -349,19 +349,21 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
                     const int32_t s = (j + t * LANES) + r * kCombineSlots;
                     if (s < cnt) {
                         const float w = BF16_OUT ? ex2_approx(s_m[s] - ref) : exp2f(s_m[s] - ref);
-                        part += o[t][r] * w;
+                        part = __fmaf_rn(o[t][r], w, part);
                     }
                 }
                 s_part[j + t * LANES][d] = part;
             }
             __syncthreads();
             if (j == 0) {
+                // Explicit roundings: the in-cluster merge of the streaming kernel performs the
+                // same operations and must give the same bits.
                 float tile_acc = s_part[0][d];
 #pragma unroll
-                for (int v = 1; v < kCombineSlots; ++v) tile_acc += s_part[v][d];
-                acc = acc * rescale + tile_acc;
+                for (int v = 1; v < kCombineSlots; ++v) tile_acc = __fadd_rn(tile_acc, s_part[v][d]);
+                acc = __fmaf_rn(acc, rescale, tile_acc);
             }
-            l_run = l_run * rescale + ltile;
+            l_run = __fmaf_rn(l_run, rescale, ltile);
             m_run = m_new;
             __syncthreads();  // the next pass overwrites s_m, s_l and s_part
         }

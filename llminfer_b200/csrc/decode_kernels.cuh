@@ -23,7 +23,7 @@ struct StreamShape {
 constexpr StreamShape kDefaultStreamShape = {4, 1, 64, 1};
 
 size_t stream_bf16_smem_bytes(int warps, int stages, int keys, int n_tiles, bool fused,
-                              int batch_for_tables);
+                              bool cluster, int batch_for_tables);
 
 // What the BF16 streaming kernel needs to run the front stage itself (QK-Norm + RoPE of the
 // raw query rows in DecodeArgs::q, and of the new key rows, which it appends to the cache
@@ -41,9 +41,15 @@ struct FusedFrontArgs {
 
 // The tensor maps must have been encoded with a box of kDefaultStreamShape.keys rows. With
 // `fused` the kernel also runs the front stage (see FusedFrontArgs). group * q_tokens <= 16.
+// With args.cluster_size > 0 the launch is one cluster of that many CTAs per unit (grid =
+// units * cluster_size) and the splits are merged inside the clusters: no combine launch.
 cudaError_t launch_stream_bf16(const CUtensorMap& tmap_k, const CUtensorMap& tmap_v,
                                const DecodeArgs& args, const FusedFrontArgs* fused, int grid,
                                cudaStream_t stream);
+// Clusters of args.cluster_size CTAs of that kernel the GPU holds at once (0: none, or the
+// query failed).
+int stream_bf16_max_clusters(const CUtensorMap& tmap_k, const CUtensorMap& tmap_v,
+                             const DecodeArgs& args, const FusedFrontArgs* fused, int grid);
 
 cudaError_t launch_stream_f32(const DecodeArgs& args, int grid, cudaStream_t stream);
 

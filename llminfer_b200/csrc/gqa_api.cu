@@ -186,7 +186,7 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
         out->num_items = (int32_t)items;
         out->num_ctas = (int32_t)(items < g_max ? (items > 0 ? items : 1) : g_max);
         out->needs_combine = ms > 1 ? 1 : 0;
-        out->reserved = 0;
+        out->cluster_size = 0;
         out->workspace_bytes = ms > 1 ? (size_t)items * rec : 0;
         if (in.workspace_bytes != 0 && out->workspace_bytes > in.workspace_bytes) {
             return GQA_ERR_WORKSPACE;
@@ -225,7 +225,41 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
     return finish(best_q);
 }
 
+// GQA_CLUSTER_MERGE=0 keeps the combine launch for every split plan (for measurements).
+bool cluster_merge_disabled() {
+    static const bool off = [] {
+        const char* v = std::getenv("GQA_CLUSTER_MERGE");
+        return v != nullptr && v[0] == '0';
+    }();
+    return off;
+}
+
+// CTAs per cluster when the splits of `plan` can be merged inside thread-block clusters (one
+// cluster per unit, one CTA per split) instead of by a combine launch: BF16, 2 to 8 splits per
+// unit even at the largest length the kernels may see, and the whole grid one wave. 0 if not.
+int32_t cluster_size_for(const gqa_decode_params* p, const gqa_decode_plan_info& plan,
+                         int32_t sm_count) {
+    if (p->dtype != GQA_DTYPE_BF16 || !plan.needs_combine || cluster_merge_disabled()) return 0;
+    int32_t c = plan.max_splits;
+    if (p->seq_lens_dev != nullptr) {
+        const int32_t cap = ceil_div(ceil_div((int32_t)capacity_of(p), kChunkKeys), plan.split_chunks);
+        c = cap > c ? cap : c;
+    }
+    if (c < 2 || c > 8) return 0;
+    const int64_t ctas = (int64_t)p->batch * p->num_kv_heads * c;
+    if (ctas > sm_count || (p->max_ctas > 0 && ctas > p->max_ctas)) return 0;
+    return c;
+}
+
+int plan_from_params_core(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out);
+
 int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out) {
+    const int rc = plan_from_params_core(p, sm_count, out);
+    if (rc == GQA_OK) out->cluster_size = cluster_size_for(p, *out, sm_count);
+    return rc;
+}
+
+int plan_from_params_core(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out) {
     PlanInput in;
     in.batch = p->batch;
     in.num_kv_heads = p->num_kv_heads;
@@ -582,6 +616,28 @@ int gqa::decode_sequence_parallel(const gqa_decode_params* p, const gqa::PeerGat
 
 namespace {
 
+// The planner's cluster size, kept only if the GPU holds all `units` clusters at once (clusters
+// are placed inside GPCs, so fewer may fit than SMs / size). Asked once per device and variant.
+int32_t confirmed_cluster_size(int32_t size, bool two_tiles, bool fused, int32_t units) {
+    static std::mutex mu;
+    static int cache[64][9][2][2];  // 0: not asked yet, else clusters + 1
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || size < 2 || size > 8) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    int& slot = cache[dev][size][two_tiles ? 1 : 0][fused ? 1 : 0];
+    if (slot == 0) {
+        gqa::DecodeArgs probe;
+        std::memset(&probe, 0, sizeof(probe));
+        probe.cluster_size = size;
+        probe.group = two_tiles ? 8 : 4;
+        probe.q_tokens = two_tiles ? 2 : 1;
+        static CUtensorMap dummy;
+        gqa::FusedFrontArgs ff = {};
+        slot = gqa::stream_bf16_max_clusters(dummy, dummy, probe, fused ? &ff : nullptr, size) + 1;
+    }
+    return slot - 1 >= units ? size : 0;
+}
+
 int decode_impl(const gqa_decode_params* p, const gqa_fused_front* front,
                 const gqa::PeerGatherArgs* gather, DecodeMode mode, float* records, bool* fused,
                 const TokenPass* pass) {
@@ -617,6 +673,17 @@ int decode_impl(const gqa_decode_params* p, const gqa_fused_front* front,
     if (rc != GQA_OK) return rc;
     const int32_t group = p->num_q_heads / p->num_kv_heads;
     const size_t rec_bytes = (size_t)group * tokens * (kHeadDim + 2) * sizeof(float);
+    // Splits merged inside thread-block clusters need no scratch and no second launch.
+    int32_t cluster = 0;
+    if (mode == DecodeMode::kOutput && gather == nullptr && plan.cluster_size > 0) {
+        cluster = confirmed_cluster_size(plan.cluster_size, group * tokens > 8, front != nullptr,
+                                         p->batch * p->num_kv_heads);
+    }
+    if (cluster > 0) {
+        plan.needs_combine = 0;
+        plan.workspace_bytes = 0;
+        plan.num_ctas = p->batch * p->num_kv_heads * cluster;
+    }
     if (by_records && !plan.needs_combine) {
         // Every unit leaves a record for the merge across slices, also when it is not split.
         plan.needs_combine = 1;
@@ -665,6 +732,7 @@ int decode_impl(const gqa_decode_params* p, const gqa_fused_front* front,
     const size_t fit = p->workspace != nullptr ? p->workspace_bytes / rec_bytes : 0;
     a.item_capacity = fit > (size_t)INT32_MAX ? INT32_MAX : (int32_t)fit;
     a.num_blocks = p->layout.num_blocks;
+    a.cluster_size = cluster;
     a.scale_log2 = (1.0f / sqrtf((float)kHeadDim)) * 1.44269504088896340736f;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(p->stream);
 

@@ -23,7 +23,11 @@
 //
 // A KV head's sum is stored in a small workspace as an 8-byte word that carries the sum and
 // the launch number (so no fence or atomic is needed), and in the sharded form pushed to
-// every rank's window in the same format (plain stores over NVLink). When a CTA has streamed
+// every rank's window in the same format (plain stores over NVLink). The words of one
+// (KV head, 16-row tile) lie together, token-major: a warp first turns its accumulator
+// fragment into that order through shared memory and then stores runs of 256 bytes, instead
+// of the 64-byte pieces the fragment layout would give (which cost most of the exchange at
+// eight ranks). When a CTA has streamed
 // all its tasks it finishes its share of the outputs: it polls (with a time limit) for the
 // words of all KV heads, adds them in ascending order and updates the residual.
 #include "../../include/gqa_b200.h"
@@ -86,6 +90,12 @@ __device__ __forceinline__ bool wait_full(uint32_t bar, uint32_t parity) {
     }
 }
 
+// Place of the sum of (KV head g, token b, output row n) among the tagged words.
+__device__ __forceinline__ int64_t word_index(const OprojArgs& a, int g, int b, int n) {
+    return ((((int64_t)g * (a.hidden / kTileRows) + (n / kTileRows)) * a.batch + b) * kTileRows) +
+           (n % kTileRows);
+}
+
 // Where output row n of token b goes, and whether the old value is added (the residual form).
 __device__ __forceinline__ __nv_bfloat16* output_at(const OprojArgs& a, int b, int n) {
     if (a.residual != nullptr) return a.residual + (int64_t)b * a.hidden + n;
@@ -108,6 +118,7 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
     __shared__ uint32_t s_step;
     __shared__ uint32_t s_local_step;
     __shared__ int s_timed_out;
+    __shared__ float s_stage[kProjMaxWarps][kProjTokens * kTileRows];
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -247,28 +258,41 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
         // acc[0..1]: row gid, tokens 2 tig and 2 tig + 1; acc[2..3]: row gid + 8. With a single
         // KV head in the whole model that is the result; otherwise each sum becomes a tagged
         // word, here or (sharded) in every rank's window, for the second phase below.
+        if (count == 1) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int b = 2 * tig + (i & 1);
-            if (b >= a.batch) continue;
-            const int n = tile * kTileRows + gid + (i >> 1) * 8;
-            const int64_t token_word = (int64_t)b * a.hidden + n;
-            if (count == 1) {
+            for (int i = 0; i < 4; ++i) {
+                const int b = 2 * tig + (i & 1);
+                if (b >= a.batch) continue;
+                const int n = tile * kTileRows + gid + (i >> 1) * 8;
                 __nv_bfloat16* out = output_at(a, b, n);
                 const float before = a.residual != nullptr ? __bfloat162float(*out) : 0.f;
                 *out = __float2bfloat16(before + (0.f + acc[i]));
-                continue;
             }
-            const int64_t word = (int64_t)lg * a.batch * a.hidden + token_word;
-            if (!SHARDED) {
-                push_word(a.words + word, local_step, __float_as_uint(acc[i]));
-            } else {
-                for (int p = 0; p < g.nranks; ++p) {
-                    push_word(window_slot(g.windows[p], step, g.nranks, g.rank, g.slot_bytes) + word,
-                              step, __float_as_uint(acc[i]));
+            continue;
+        }
+        // Fragment order -> [token][row] through shared memory, then contiguous runs.
+        float* stage = s_stage[warp];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            stage[(2 * tig + (i & 1)) * kTileRows + gid + (i >> 1) * 8] = acc[i];
+        }
+        __syncwarp();
+        const int nwords = a.batch * kTileRows;
+        const int64_t base = word_index(a, lg, 0, tile * kTileRows);
+        if (!SHARDED) {
+            for (int w = lane; w < nwords; w += 32) {
+                push_word(a.words + base + w, local_step, __float_as_uint(stage[w]));
+            }
+        } else {
+            for (int p = 0; p < g.nranks; ++p) {
+                unsigned long long* dst =
+                    window_slot(g.windows[p], step, g.nranks, g.rank, g.slot_bytes) + base;
+                for (int w = lane; w < nwords; w += 32) {
+                    push_word(dst + w, step, __float_as_uint(stage[w]));
                 }
             }
         }
+        __syncwarp();  // the next tile overwrites the staging row
     }
 
     // ---- second phase: every CTA finishes its share of the outputs -----------------------
@@ -279,9 +303,10 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
         const int64_t outputs = (int64_t)a.batch * a.hidden;
         for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < outputs && !timed_out;
              o += (int64_t)gridDim.x * blockDim.x) {
+            const int ob = (int)(o / a.hidden), on = (int)(o % a.hidden);
             auto word_at = [&](int idx, uint32_t* tag) -> const unsigned long long* {
                 const int r = idx / a.groups;
-                const int64_t word = (int64_t)(idx - r * a.groups) * outputs + o;
+                const int64_t word = word_index(a, idx - r * a.groups, ob, on);
                 if (SHARDED) {
                     *tag = step;
                     return window_slot(g.windows[g.rank], step, g.nranks, r, g.slot_bytes) + word;
@@ -289,7 +314,7 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
                 *tag = local_step;
                 return a.words + word;
             };
-            __nv_bfloat16* out = output_at(a, (int)(o / a.hidden), (int)(o % a.hidden));
+            __nv_bfloat16* out = output_at(a, ob, on);
             // The old value travels while the words are polled.
             const float before = a.residual != nullptr ? __bfloat162float(*out) : 0.f;
             float total = 0.f;
@@ -421,20 +446,6 @@ int run(const gqa_oproj_params* p, const SplitOut* split, gqa_comm* comm) {
     const int tiles = p->hidden / kTileRows;
     int stages = 0, ctas_per_sm = 0;
     oproj_shape(&stages, &ctas_per_sm);
-    // Every warp gets the same number of tiles (k) of its KV head, or one fewer: as many
-    // warps as the GPU holds at once, but no more than tiles; small problems use narrower
-    // CTAs so that they still reach every SM.
-    int ctas_per_group = ctas_per_sm * sms / groups;
-    if (ctas_per_group < 1) ctas_per_group = 1;
-    const int k = (tiles + ctas_per_group * kProjMaxWarps - 1) / (ctas_per_group * kProjMaxWarps);
-    const int workers = (tiles + k - 1) / k;  // per KV head
-    int warps = kProjMaxWarps;
-    if ((int64_t)workers * groups < (int64_t)sms * kProjMaxWarps) {
-        warps = (int)((int64_t)workers * groups / sms);
-        if (warps < 1) warps = 1;
-    }
-    const int grid = (workers + warps - 1) / warps * groups;
-    const size_t smem = smem_bytes(warps, stages, per_group);
     // The shared-memory limit is a per-device property of the kernels: raise it once per device.
     {
         static std::mutex mu;
@@ -453,6 +464,36 @@ int run(const gqa_oproj_params* p, const SplitOut* split, gqa_comm* comm) {
             raised[dev] = true;
         }
     }
+    // Every CTA of the grid waits, in its finishing phase, for words written by the others:
+    // the whole grid must be resident at once. Wide groups need more shared memory per CTA,
+    // so fewer CTAs fit an SM than the tuned number: ask the runtime.
+    {
+        const size_t full = smem_bytes(kProjMaxWarps, stages, per_group);
+        if (full > (size_t)kMaxSmem) return GQA_ERR_SHAPE;
+        int fit = 0;
+        const cudaError_t oe =
+            comm != nullptr && gqa_comm_nranks(comm) > 1
+                ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fit, oproj_residual_kernel<true>,
+                                                                kProjMaxWarps * 32, full)
+                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&fit, oproj_residual_kernel<false>,
+                                                                kProjMaxWarps * 32, full);
+        if (oe != cudaSuccess || fit < 1) return GQA_ERR_CUDA;
+        if (ctas_per_sm > fit) ctas_per_sm = fit;
+    }
+    // Every warp gets the same number of tiles (k) of its KV head, or one fewer: as many
+    // warps as the GPU holds at once, but no more than tiles; small problems use narrower
+    // CTAs so that they still reach every SM.
+    int ctas_per_group = ctas_per_sm * sms / groups;
+    if (ctas_per_group < 1) ctas_per_group = 1;
+    const int k = (tiles + ctas_per_group * kProjMaxWarps - 1) / (ctas_per_group * kProjMaxWarps);
+    const int workers = (tiles + k - 1) / k;  // per KV head
+    int warps = kProjMaxWarps;
+    if ((int64_t)workers * groups < (int64_t)sms * kProjMaxWarps) {
+        warps = (int)((int64_t)workers * groups / sms);
+        if (warps < 1) warps = 1;
+    }
+    const int grid = (workers + warps - 1) / warps * groups;
+    const size_t smem = smem_bytes(warps, stages, per_group);
     if (smem > (size_t)kMaxSmem) return GQA_ERR_SHAPE;
     CUtensorMap wmap;
     const int mrc = cached_matrix_map(p->weight, (int64_t)p->num_q_heads * kHeadDim, p->hidden,

@@ -61,6 +61,7 @@ struct DecodeArgs {
     int32_t len_capacity;       // keys a sequence can hold (device lengths are clamped to it)
     int32_t item_capacity;      // partial records the scratch can hold
     int32_t num_blocks;         // blocks in the cache (block ids are checked against it)
+    int32_t cluster_size;       // > 0: one thread-block cluster per unit, one CTA per split
     float scale_log2;  // (1 / sqrt(head_dim)) * log2(e)
 };
 
@@ -164,6 +165,28 @@ __device__ inline Item decode_item(const DecodeArgs& a, const WorkTables& t, int
     it.chunk_begin = it.split * a.split_chunks;
     it.chunk_end = min(chunks, it.chunk_begin + a.split_chunks);
     return it;
+}
+
+// Cluster launches: the cluster is the unit (sequence-major, then kv head), the CTA's rank in
+// it is the split. False when the unit has fewer splits than the cluster has CTAs and this CTA
+// has nothing to stream. A unit with more splits than CTAs (device lengths outgrew the plan)
+// is cut off at the last CTA and reported.
+__device__ inline bool cluster_item(const DecodeArgs& a, const WorkTables& t, Item* it) {
+    const int32_t unit = blockIdx.x / a.cluster_size;
+    it->split = blockIdx.x - unit * a.cluster_size;
+    it->b = unit / a.num_kv_heads;
+    it->hk = unit - it->b * a.num_kv_heads;
+    it->len = t.s_len != nullptr ? t.s_len[it->b] : a.uniform_len;
+    const int32_t chunks = ceil_div(it->len, kChunkKeys);
+    int32_t nsplits = ceil_div(chunks, a.split_chunks);
+    if (nsplits > a.cluster_size) {
+        if (threadIdx.x == 0 && it->split == 0) raise_status(a, kStatusBadInput);
+        nsplits = a.cluster_size;
+    }
+    it->nsplits = nsplits;
+    it->chunk_begin = it->split * a.split_chunks;
+    it->chunk_end = min(chunks, it->chunk_begin + a.split_chunks);
+    return it->split < nsplits;
 }
 
 // First item and split count of unit (b, hk), for the combine kernel.

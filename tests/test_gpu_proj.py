@@ -218,3 +218,20 @@ def test_qkv_rejects_unsupported_shapes(gqa):
     w2 = torch.zeros(3 * 128, 2048, dtype=torch.bfloat16, device="cuda:0")
     with pytest.raises(gqa.GqaError):
         gqa.qkv_gemv(x2, w2, q, q.clone(), q.clone())   # two column groups: workspace missing
+
+
+def test_wide_groups_on_a_large_matrix_stay_resident(gqa):
+    """Sixteen heads per KV head need so much shared memory per CTA that fewer CTAs fit an SM
+    than the tuned number; with a large output dimension the grid would then exceed what the
+    GPU holds at once, and its CTAs, which wait for one another's sums, would time out. The
+    launcher sizes the grid from the occupancy the runtime reports."""
+    rng = np.random.default_rng(77)
+    batch, heads, kv_heads, n = 2, 32, 2, 12288
+    k = heads * 128
+    x = cases.to_bf16_bits(rng.standard_normal((batch, k), dtype=np.float32))
+    w = cases.to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32) / np.float32(np.sqrt(k)))
+    r = cases.to_bf16_bits(rng.standard_normal((batch, n), dtype=np.float32))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    got = run(gqa, x, w, r, kv_heads=kv_heads, status=status)
+    assert int(status.item()) == 0
+    check(got, oracle.gemv_add(x, w, r, accum=1), "fp64 oracle")
