@@ -186,6 +186,13 @@ typedef struct gqa_decode_plan_info {
  */
 int gqa_decode_plan(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out);
 
+/*
+ * How many thread-block clusters of `cluster_size` CTAs (2 .. 16) of the BF16 streaming kernel
+ * the current GPU holds at once; 0 when it takes none of that size. The planner merges splits
+ * inside clusters only when every (sequence, kv head) unit gets its cluster in one wave.
+ */
+int32_t gqa_cluster_capacity(int32_t cluster_size);
+
 /* Launches the attention kernels on p->stream. Asynchronous. */
 int gqa_decode(const gqa_decode_params* p);
 

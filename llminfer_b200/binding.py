@@ -169,6 +169,7 @@ _SIGNATURES = {
     "gqa_layout_pool": (C.c_int, [C.c_int32] * 4 + [C.POINTER(_Layout)]),
     "gqa_decode_plan": (C.c_int, [C.POINTER(_DecodeParams), C.c_int32, C.POINTER(_PlanInfo)]),
     "gqa_decode": (C.c_int, [C.POINTER(_DecodeParams)]),
+    "gqa_cluster_capacity": (C.c_int32, [C.c_int32]),
     "gqa_decode_static_scratch": (C.c_int, [C.POINTER(_DecodeParams)]),
     "gqa_decode_fused": (C.c_int, [C.POINTER(_DecodeParams), C.POINTER(_FusedFront)]),
     "gqa_decode_partial": (C.c_int, [C.POINTER(_DecodeParams), C.c_void_p]),

@@ -39,7 +39,7 @@
 // in HBM. Nothing else in the launch reads those cache rows, so no ordering between CTAs is
 // needed.
 //
-// CLUSTER launches one thread-block cluster per unit with one CTA per split (at most 8): each
+// CLUSTER launches one thread-block cluster per unit with one CTA per split (at most 16): each
 // CTA streams its split, leaves its (O, m, l) in its own shared memory, and after a cluster
 // barrier the CTAs of the cluster merge the splits by reading one another's shared memory
 // (distributed shared memory) and write the final rows. Short contexts, where the whole launch
@@ -604,9 +604,10 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                  idx += csize * (WARPS * 32)) {
                 const int n = idx >> 7;
                 const int d = idx & (kHeadDim - 1);
-                float ms[8], ls[8], os[8];
+                constexpr int kMaxSplits = 16;
+                float ms[kMaxSplits], ls[kMaxSplits], os[kMaxSplits];
 #pragma unroll
-                for (int sp = 0; sp < 8; ++sp) {
+                for (int sp = 0; sp < kMaxSplits; ++sp) {
                     if (sp < own.nsplits) {
                         const uint32_t base = cluster_map(rec_base, (uint32_t)sp);
                         ms[sp] = ld_cluster_f32(base + (cols * kHeadDim + n) * 4);
@@ -618,17 +619,24 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                 }
                 float tmax = ms[0];
 #pragma unroll
-                for (int sp = 1; sp < 8; ++sp) tmax = fmaxf(tmax, ms[sp]);
+                for (int sp = 1; sp < kMaxSplits; ++sp) tmax = fmaxf(tmax, ms[sp]);
                 const float ref = safe_max(tmax);
-                float ltile = 0.0f, acc = 0.0f;
+                float wgt[kMaxSplits];
+                float ltile = 0.0f;
 #pragma unroll
-                for (int sp = 0; sp < 8; ++sp) {
-                    if (sp < own.nsplits) {
-                        const float wgt = ex2_approx(ms[sp] - ref);
-                        ltile = __fmaf_rn(ls[sp], wgt, ltile);
-                        const float part = __fmaf_rn(os[sp], wgt, 0.0f);
-                        acc = sp == 0 ? part : __fadd_rn(acc, part);
-                    }
+                for (int sp = 0; sp < kMaxSplits; ++sp) {
+                    wgt[sp] = ex2_approx(ms[sp] - ref);
+                    if (sp < own.nsplits) ltile = __fmaf_rn(ls[sp], wgt[sp], ltile);
+                }
+                // Eight slots (split s in slot s % 8, ascending inside a slot), slots added in
+                // ascending order: the combine kernel's order for up to 32 splits.
+                float acc = 0.0f;
+#pragma unroll
+                for (int slot = 0; slot < 8; ++slot) {
+                    float part = 0.0f;
+                    if (slot < own.nsplits) part = __fmaf_rn(os[slot], wgt[slot], part);
+                    if (slot + 8 < own.nsplits) part = __fmaf_rn(os[slot + 8], wgt[slot + 8], part);
+                    acc = slot == 0 ? part : __fadd_rn(acc, part);
                 }
                 const int t = n / group;
                 const int64_t row = (((int64_t)own.b * a.q_token_stride + a.q_token_first + t) *
@@ -675,6 +683,16 @@ static cudaError_t launch_variant(const CUtensorMap& tk, const CUtensorMap& tv,
             e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;
             if (dev >= 0 && dev < 64) configured[dev] = smem;
+        }
+    }
+    if (CLUSTER && args.cluster_size > 8) {
+        // Clusters of more than 8 CTAs are not portable across GPUs: ask for them explicitly.
+        static bool allowed[64] = {};
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev < 0 || dev >= 64 || !allowed[dev]) {
+            e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (e != cudaSuccess) return e;
+            if (dev >= 0 && dev < 64) allowed[dev] = true;
         }
     }
     cudaLaunchAttribute attrs[2];

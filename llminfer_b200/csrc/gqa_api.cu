@@ -131,6 +131,7 @@ gqa::StreamShape stream_shape() { return gqa::kDefaultStreamShape; }
 constexpr double kItemOverhead = 1.0;
 constexpr double kCombineBase = 3.0;
 constexpr double kCombinePerSplit = 0.05;
+constexpr double kClusterMerge = 1.0;  // cluster barrier + merge through distributed shared memory
 
 struct PlanInput {
     int32_t batch;
@@ -144,7 +145,12 @@ struct PlanInput {
     size_t workspace_bytes;  // 0 = unconstrained
     int32_t chunk_align;     // splits start on multiples of this many chunks
     double overhead_scale;   // fixed costs relative to one step (a CUDA-core FP32 step is long)
+    // Splits merged inside thread-block clusters (one cluster per unit, one CTA per split):
+    const int32_t* cluster_fit;  // [17] clusters of each size the GPU holds at once; null = never
+    int32_t cluster_chunks;      // chunks of the longest sequence the kernels may ever see
 };
+
+constexpr int kMaxClusterSize = 16;  // 8 is the portable limit; up to 16 where the GPU takes it
 
 int64_t items_for(const PlanInput& in, int32_t q, int32_t* max_splits) {
     int64_t items = 0;
@@ -175,6 +181,18 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
     }
     const int32_t g_max = in.max_ctas > 0 && in.max_ctas < in.sm_count ? in.max_ctas : in.sm_count;
     const size_t rec = record_bytes(in.group);
+    const int64_t units = (int64_t)in.batch * in.num_kv_heads;
+
+    // CTAs per cluster if splits of q chunks can be merged inside clusters: 2 to 16 splits per
+    // unit even at the largest length the kernels may see, the whole grid one wave, and every
+    // cluster resident at once. 0 if not.
+    auto cluster_for = [&](int32_t q) -> int32_t {
+        if (in.cluster_fit == nullptr) return 0;
+        const int32_t c = ceil_div(in.cluster_chunks > max_chunks ? in.cluster_chunks : max_chunks, q);
+        if (c < 2 || c > kMaxClusterSize) return 0;
+        if (units * c > g_max || units > in.cluster_fit[c]) return 0;
+        return c;
+    };
 
     auto finish = [&](int32_t q) -> int {
         q = ceil_div(q < 1 ? 1 : q, in.chunk_align) * in.chunk_align;
@@ -186,7 +204,7 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
         out->num_items = (int32_t)items;
         out->num_ctas = (int32_t)(items < g_max ? (items > 0 ? items : 1) : g_max);
         out->needs_combine = ms > 1 ? 1 : 0;
-        out->cluster_size = 0;
+        out->cluster_size = ms > 1 ? cluster_for(q) : 0;
         out->workspace_bytes = ms > 1 ? (size_t)items * rec : 0;
         if (in.workspace_bytes != 0 && out->workspace_bytes > in.workspace_bytes) {
             return GQA_ERR_WORKSPACE;
@@ -204,7 +222,7 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
     bool have = false;
     int32_t last_q = -1;
     for (int32_t s = 1; s <= max_chunks; ++s) {
-        const int32_t q = ceil_div(max_chunks, s);
+        const int32_t q = ceil_div(ceil_div(max_chunks, s), in.chunk_align) * in.chunk_align;
         if (q == last_q) continue;
         last_q = q;
         int32_t ms = 0;
@@ -213,7 +231,10 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
         const int64_t rounds = (items + g_max - 1) / g_max;
         double cost = (double)rounds *
                       ((double)ceil_div(q, kPlanWarps) + in.overhead_scale * kItemOverhead);
-        if (ms > 1) cost += in.overhead_scale * (kCombineBase + kCombinePerSplit * ms);
+        if (ms > 1) {
+            cost += in.overhead_scale *
+                    (cluster_for(q) > 0 ? kClusterMerge : kCombineBase + kCombinePerSplit * ms);
+        }
         if (!have || cost < best_cost - 1e-9) {
             best_cost = cost;
             best_q = q;
@@ -234,32 +255,47 @@ bool cluster_merge_disabled() {
     return off;
 }
 
-// CTAs per cluster when the splits of `plan` can be merged inside thread-block clusters (one
-// cluster per unit, one CTA per split) instead of by a combine launch: BF16, 2 to 8 splits per
-// unit even at the largest length the kernels may see, and the whole grid one wave. 0 if not.
-int32_t cluster_size_for(const gqa_decode_params* p, const gqa_decode_plan_info& plan,
-                         int32_t sm_count) {
-    if (p->dtype != GQA_DTYPE_BF16 || !plan.needs_combine || cluster_merge_disabled()) return 0;
-    int32_t c = plan.max_splits;
-    if (p->seq_lens_dev != nullptr) {
-        const int32_t cap = ceil_div(ceil_div((int32_t)capacity_of(p), kChunkKeys), plan.split_chunks);
-        c = cap > c ? cap : c;
+// How many clusters of each size (2 .. 16 CTAs of the BF16 streaming kernel) the GPU holds at
+// once. Asked from the current device when it is the one being planned for (clusters are placed
+// inside GPCs, so fewer may fit than SMs / size); otherwise SMs / size for the portable sizes.
+const int32_t* cluster_fit_table(int32_t sm_count) {
+    static std::mutex mu;
+    static int32_t device_tables[64][kMaxClusterSize + 1];
+    static bool ready[64] = {};
+    thread_local int32_t guess[kMaxClusterSize + 1];
+    int dev = -1, dev_sms = 0;
+    const bool on_device = cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 &&
+                           cudaDeviceGetAttribute(&dev_sms, cudaDevAttrMultiProcessorCount, dev) ==
+                               cudaSuccess && dev_sms == sm_count;
+    if (!on_device) {
+        cudaGetLastError();
+        for (int c = 0; c <= kMaxClusterSize; ++c) guess[c] = c >= 2 && c <= 8 ? sm_count / c : 0;
+        return guess;
     }
-    if (c < 2 || c > 8) return 0;
-    const int64_t ctas = (int64_t)p->batch * p->num_kv_heads * c;
-    if (ctas > sm_count || (p->max_ctas > 0 && ctas > p->max_ctas)) return 0;
-    return c;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ready[dev]) {
+        static CUtensorMap dummy;
+        for (int c = 0; c <= kMaxClusterSize; ++c) {
+            device_tables[dev][c] = 0;
+            if (c < 2) continue;
+            gqa::DecodeArgs probe;
+            std::memset(&probe, 0, sizeof(probe));
+            probe.cluster_size = c;
+            probe.group = 8;  // the variant with the largest shared-memory footprint
+            probe.q_tokens = 2;
+            gqa::FusedFrontArgs ff = {};
+            device_tables[dev][c] = gqa::stream_bf16_max_clusters(dummy, dummy, probe, &ff, c);
+        }
+        ready[dev] = true;
+    }
+    return device_tables[dev];
 }
 
-int plan_from_params_core(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out);
+int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out,
+                     bool allow_cluster = true);
 
-int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out) {
-    const int rc = plan_from_params_core(p, sm_count, out);
-    if (rc == GQA_OK) out->cluster_size = cluster_size_for(p, *out, sm_count);
-    return rc;
-}
-
-int plan_from_params_core(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out) {
+int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out,
+                     bool allow_cluster) {
     PlanInput in;
     in.batch = p->batch;
     in.num_kv_heads = p->num_kv_heads;
@@ -279,6 +315,13 @@ int plan_from_params_core(const gqa_decode_params* p, int32_t sm_count, gqa_deco
     // The FP32 kernel spends roughly ten times longer on a chunk than the BF16 one, so the
     // fixed costs weigh a tenth as much there and finer splits pay off.
     in.overhead_scale = p->dtype == GQA_DTYPE_F32 ? 0.1 : 1.0;
+    in.cluster_fit = nullptr;
+    in.cluster_chunks = 0;
+    if (allow_cluster && p->dtype == GQA_DTYPE_BF16 && !cluster_merge_disabled()) {
+        in.cluster_fit = cluster_fit_table(sm_count);
+        // Lengths read from the device may grow up to the capacity: size the clusters for it.
+        if (p->seq_lens_dev != nullptr) in.cluster_chunks = ceil_div((int32_t)capacity, kChunkKeys);
+    }
     if (p->block_table_dev != nullptr && p->blocks_per_seq > 1 &&
         p->layout.block_tokens % stage_keys != 0) {
         return GQA_ERR_SHAPE;
@@ -555,7 +598,25 @@ int gqa_decode_plan(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pla
     gqa_decode_params planned = *p;
     const int32_t per_pass = kMaxColumns / (p->num_q_heads / p->num_kv_heads);
     if (tokens_of(p) > per_pass) planned.q_tokens = per_pass;
-    return plan_from_params(&planned, sm_count, out);
+    rc = plan_from_params(&planned, sm_count, out);
+    if (rc == GQA_OK && out->cluster_size > 0) {
+        // gqa_decode merges these splits inside clusters and needs no workspace; the calls that
+        // cannot (gathers, records) cut the keys as if clusters did not exist: report the
+        // larger of the two workspaces so that one allocation serves them all.
+        gqa_decode_plan_info plain;
+        if (plan_from_params(&planned, sm_count, &plain, false) == GQA_OK &&
+            plain.workspace_bytes > out->workspace_bytes) {
+            out->workspace_bytes = plain.workspace_bytes;
+        }
+    }
+    return rc;
+}
+
+int32_t gqa_cluster_capacity(int32_t cluster_size) {
+    if (cluster_size < 2 || cluster_size > kMaxClusterSize) return 0;
+    int32_t sms = 0;
+    if (device_sm_count(&sms) != GQA_OK) return 0;
+    return cluster_fit_table(sms)[cluster_size];
 }
 
 int gqa_decode(const gqa_decode_params* p) {
@@ -616,28 +677,6 @@ int gqa::decode_sequence_parallel(const gqa_decode_params* p, const gqa::PeerGat
 
 namespace {
 
-// The planner's cluster size, kept only if the GPU holds all `units` clusters at once (clusters
-// are placed inside GPCs, so fewer may fit than SMs / size). Asked once per device and variant.
-int32_t confirmed_cluster_size(int32_t size, bool two_tiles, bool fused, int32_t units) {
-    static std::mutex mu;
-    static int cache[64][9][2][2];  // 0: not asked yet, else clusters + 1
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || size < 2 || size > 8) return 0;
-    std::lock_guard<std::mutex> lock(mu);
-    int& slot = cache[dev][size][two_tiles ? 1 : 0][fused ? 1 : 0];
-    if (slot == 0) {
-        gqa::DecodeArgs probe;
-        std::memset(&probe, 0, sizeof(probe));
-        probe.cluster_size = size;
-        probe.group = two_tiles ? 8 : 4;
-        probe.q_tokens = two_tiles ? 2 : 1;
-        static CUtensorMap dummy;
-        gqa::FusedFrontArgs ff = {};
-        slot = gqa::stream_bf16_max_clusters(dummy, dummy, probe, fused ? &ff : nullptr, size) + 1;
-    }
-    return slot - 1 >= units ? size : 0;
-}
-
 int decode_impl(const gqa_decode_params* p, const gqa_fused_front* front,
                 const gqa::PeerGatherArgs* gather, DecodeMode mode, float* records, bool* fused,
                 const TokenPass* pass) {
@@ -668,17 +707,14 @@ int decode_impl(const gqa_decode_params* p, const gqa_fused_front* front,
     {
         gqa_decode_params planned = *p;
         planned.q_tokens = tokens;
-        rc = plan_from_params(&planned, sms, &plan);
+        // Splits can be merged inside thread-block clusters (no scratch, no second launch)
+        // unless the merged rows have to leave through a gather or as records.
+        rc = plan_from_params(&planned, sms, &plan, mode == DecodeMode::kOutput && gather == nullptr);
     }
     if (rc != GQA_OK) return rc;
     const int32_t group = p->num_q_heads / p->num_kv_heads;
     const size_t rec_bytes = (size_t)group * tokens * (kHeadDim + 2) * sizeof(float);
-    // Splits merged inside thread-block clusters need no scratch and no second launch.
-    int32_t cluster = 0;
-    if (mode == DecodeMode::kOutput && gather == nullptr && plan.cluster_size > 0) {
-        cluster = confirmed_cluster_size(plan.cluster_size, group * tokens > 8, front != nullptr,
-                                         p->batch * p->num_kv_heads);
-    }
+    const int32_t cluster = plan.cluster_size;
     if (cluster > 0) {
         plan.needs_combine = 0;
         plan.workspace_bytes = 0;
