@@ -163,10 +163,10 @@ class ClockSampler:
 
 
 # DRAM traffic per algorithmic byte of the streaming kernel, from one ncu capture
-# (profiles/ncu_full_gqa_decode_stream_bf16_b1_ctx131072.md: 536.94 MB read + 3.83 MB written
+# (profiles/ncu_full_gqa_decode_stream_bf16_b1_ctx131072.md: 536.96 MB read + 3.60 MB written
 # for 536.90 MB algorithmic). Traffic grows in proportion to the keys processed, so the
 # capture of the batch-1 case is scaled by the algorithmic bytes of the workload timed here.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = (536.942336 + 3.828480) / 536.903680
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = (536.962816 + 3.600384) / 536.903680
 
 
 def measured_peak_gbs() -> tuple[float, str]:

@@ -255,8 +255,11 @@ int gqa_merge_partials(const float* records, int32_t nparts, int64_t rows, int32
  * it until the process exits). The call allocates and frees no device memory.
  *   - The first call on a device looks up the array's device address
  *     (cudaGetSymbolAddress); make that first call outside any stream capture.
- *   - A plan that needs more than GQA_STATIC_SCRATCH_BYTES (a very small explicit split_keys
- *     on a very long context) returns GQA_ERR_WORKSPACE and launches nothing.
+ *   - The planner keeps its split within GQA_STATIC_SCRATCH_BYTES (coarsening it when lengths
+ *     are known on the device only and records are sized for full sequences); an explicit
+ *     split_keys whose records cannot fit returns GQA_ERR_WORKSPACE and launches nothing.
+ *     Device-side lengths that outgrow the plan make the kernels skip the records that would
+ *     not fit and set *status_dev to GQA_STATUS_BAD_INPUT; nothing is written past the array.
  *   - All calls on one device share the array. Calls that can overlap on the GPU (different
  *     streams, concurrent graph launches) race on it: serialise them, or use gqa_decode() with
  *     one workspace each. Nothing in the array has to be cleared between calls.

@@ -14,9 +14,12 @@
 // cudaGetSymbolAddress, once per device, with that device current, and that address is what
 // the kernels receive.
 //
-// Limits. A request whose split plan needs more than GQA_STATIC_SCRATCH_BYTES (only possible
-// with a very small explicit split_keys on a very long context) is refused with
-// GQA_ERR_WORKSPACE. All calls on a device share the one array: calls that may run
+// Limits. The planner keeps its split inside GQA_STATIC_SCRATCH_BYTES (with lengths known on
+// the device only it sizes the records for full sequences and coarsens the split until they
+// fit); an explicit split_keys whose records cannot fit is refused with GQA_ERR_WORKSPACE and
+// nothing is launched. If device-side lengths outgrow what the plan provided for, the kernels
+// skip the records that would fall outside the array and set the caller's status word to
+// GQA_STATUS_BAD_INPUT: they never write past it. All calls on a device share the one array: calls that may run
 // concurrently on the GPU (different streams, or graphs launched side by side) race on it and
 // must be serialised by the caller or use gqa_decode() with separate workspaces. The array keeps
 // the previous call's records; nothing in it has to start at zero, because every record that is
