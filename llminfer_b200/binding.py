@@ -520,6 +520,7 @@ class Session:
         _check(lib().gqa_session_create(DTYPE_BF16, max_batch, num_q_heads, num_kv_heads,
                                         head_dim, max_seq_len, C.byref(self._h)),
                "gqa_session_create")
+        self._marshal = {}
 
     def step(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
              qk_weight: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -527,19 +528,33 @@ class Session:
              block_table: Optional[torch.Tensor] = None, fixed_block: int = 0,
              comm: Optional["ShardComm"] = None) -> None:
         """With `comm`, out_host is the gathered [nranks, batch, local_q_heads, 128] output."""
-        lay = layout.c()
-        pos = _int_array(positions)
+        # The marshalled layout and positions are kept between steps: a decode loop passes the
+        # same layout every step, and the same positions for every layer of a token.
+        cache = self._marshal
+        if cache.get("layout_key") is not layout:
+            cache["layout_key"], cache["layout"] = layout, layout.c()
+        key = tuple(positions)
+        if cache.get("pos_key") != key:
+            cache["pos_key"], cache["pos"] = key, _int_array(positions)
+        lay, pos = cache["layout"], cache["pos"]
         bps = 0 if block_table is None else block_table.shape[1]
+        table = None if block_table is None else block_table.data_ptr()
+        handle = lib()
         if comm is None:
-            _check(lib().gqa_session_step(self._h, q_host.shape[0], _ptr(q_host), _ptr(k_host),
-                                          _ptr(v_host), _ptr(qk_weight), _ptr(k_cache),
-                                          _ptr(v_cache), C.byref(lay), pos, _ptr(block_table),
-                                          bps, fixed_block, _ptr(out_host)), "gqa_session_step")
+            rc = handle.gqa_session_step(self._h, q_host.shape[0], q_host.data_ptr(),
+                                         k_host.data_ptr(), v_host.data_ptr(),
+                                         qk_weight.data_ptr(), k_cache.data_ptr(),
+                                         v_cache.data_ptr(), C.byref(lay), pos, table, bps,
+                                         fixed_block, out_host.data_ptr())
+            if rc != 0:
+                raise GqaError(rc, "gqa_session_step")
         else:
-            _check(lib().gqa_session_step_sharded(
-                self._h, comm._h, q_host.shape[0], _ptr(q_host), _ptr(k_host), _ptr(v_host),
-                _ptr(qk_weight), _ptr(k_cache), _ptr(v_cache), C.byref(lay), pos,
-                _ptr(block_table), bps, fixed_block, _ptr(out_host)), "gqa_session_step_sharded")
+            rc = handle.gqa_session_step_sharded(
+                self._h, comm._h, q_host.shape[0], q_host.data_ptr(), k_host.data_ptr(),
+                v_host.data_ptr(), qk_weight.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                C.byref(lay), pos, table, bps, fixed_block, out_host.data_ptr())
+            if rc != 0:
+                raise GqaError(rc, "gqa_session_step_sharded")
 
     def last_timing(self) -> dict:
         """Host-side nanoseconds of the last step: staging, launches, wait, copy-out."""

@@ -391,6 +391,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
                             const_cast<void*>(a.v_cache)) + cache_off)[lane] = vv;
                     }
                 }
+                fence_proxy_async();  // these writes precede the next bulk copy into the stage
                 __syncwarp();
             }
 
