@@ -113,6 +113,38 @@ def main() -> None:
     for _ in range(5):
         again = run(q_l, k_l, v_l, per_q, per_kv, sharded=True)
         assert torch.equal(again.view(torch.int16), full.view(torch.int16)), "peer gather != unsharded"
+    # The front stage inside the sharded attention kernel (gqa_decode_sharded_fused) against
+    # the front kernel followed by gqa_decode_sharded: same gathered bits, same cache rows.
+    layout_f = gqa.layout_pool(num_blocks, block_tokens, per_kv)
+    kn = H.rand_bits(rng, (batch, hkv, d))[:, rank * per_kv:(rank + 1) * per_kv]
+    vn = H.rand_bits(rng, (batch, hkv, d))[:, rank * per_kv:(rank + 1) * per_kv]
+    wq = H.bf16_tensor(cases.to_bf16_bits(1.0 + 0.05 * rng.standard_normal(2 * d, dtype=np.float32)), dev)
+    dtab, dlens = torch.from_numpy(table).to(dev), torch.tensor(lens, dtype=torch.int32, device=dev)
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    results = []
+    for fused in (False, True):
+        dq = H.bf16_tensor(np.ascontiguousarray(q_l), dev)
+        dk, dv = H.bf16_tensor(k_l, dev), H.bf16_tensor(v_l, dev)
+        dkn, dvn = H.bf16_tensor(np.ascontiguousarray(kn), dev), H.bf16_tensor(np.ascontiguousarray(vn), dev)
+        out = torch.zeros(batch, per_q, d, dtype=torch.bfloat16, device=dev)
+        gathered = torch.zeros(world, batch, per_q, d, dtype=torch.bfloat16, device=dev)
+        kw = dict(num_kv_heads=per_kv, layout=layout_f, seq_lens=lens, seq_lens_dev=dlens,
+                  block_table=dtab, workspace=gqa.binding.workspace_for(batch, per_q, per_kv, dev),
+                  split_keys=512, status=st)
+        if fused:
+            kw["front"] = gqa.FusedFront(dkn, dvn, wq)
+        else:
+            gqa.qk_norm_rope_append(dq, dkn, dvn, wq, dk, dv, layout=layout_f,
+                                    positions=[n - 1 for n in lens],
+                                    positions_dev=torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=dev),
+                                    block_table=dtab)
+        gqa.decode_sharded(comm, gathered, dq, dk, dv, out, **kw)
+        torch.cuda.synchronize()
+        results.append((gathered, dk, dv))
+    assert int(st.item()) == 0
+    for a_, b_ in zip(results[0], results[1]):
+        assert torch.equal(a_.view(torch.int16), b_.view(torch.int16)), "fused sharded front differs"
+
     send = torch.zeros(1024, dtype=torch.int32, device=dev)
     recv = torch.zeros(world, 1024, dtype=torch.int32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)

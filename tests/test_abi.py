@@ -209,6 +209,37 @@ def test_planner_device_lengths_size_the_scratch_for_full_sequences(gqa):
     assert p["workspace_bytes"] == full_items * 4 * 130 * 4
 
 
+def test_planner_coarsens_a_hinted_split_that_the_scratch_cannot_hold(gqa):
+    """Lengths on the device only: the hint asks for a fine split, the records are sized for
+    full sequences, and a scratch too small for that split gets a coarser one, not an error."""
+    layout = gqa.layout_pool(16 * 32, 256, 8)
+    kw = dict(dtype=2, batch=16, num_q_heads=32, num_kv_heads=8, layout=layout, seq_lens=None,
+              paged=True, blocks_per_seq=32, device_lens=True, plan_len_hint=512)
+    free = gqa.decode_plan(**kw)
+    small = free["workspace_bytes"] // 3
+    tight = gqa.decode_plan(workspace_bytes=small, **kw)
+    assert tight["workspace_bytes"] <= small
+    assert tight["split_chunks"] > free["split_chunks"]
+    assert tight["num_items"] == 16 * 8 * -(-(32 * 256 // 32) // tight["split_chunks"])
+    with pytest.raises(gqa.GqaError) as e:  # an explicit split is never changed
+        gqa.decode_plan(workspace_bytes=small, split_keys=free["split_chunks"] * 32, **kw)
+    assert e.value.status == -6
+
+
+def test_planner_offers_cluster_merge_for_short_contexts_only(gqa):
+    """One cluster per unit, one CTA per split: offered when every unit has 2..16 splits and the
+    grid is one wave (without a GPU to ask, for the portable sizes up to 8 only)."""
+    short = plan(gqa, seq_lens=[1024])
+    assert short["needs_combine"] == 1 and 2 <= short["cluster_size"] <= 8
+    assert short["cluster_size"] == short["max_splits"] and 8 * short["cluster_size"] <= 148
+    assert short["workspace_bytes"] > 0  # still reported: gathers and records need it
+    long = plan(gqa, seq_lens=[131072])
+    assert long["needs_combine"] == 1 and long["cluster_size"] == 0
+    assert plan(gqa, seq_lens=[96])["cluster_size"] == 0  # not split at all
+    assert plan(gqa, dtype=1, seq_lens=[1024])["cluster_size"] == 0  # FP32 path
+    assert gqa.lib().gqa_cluster_capacity(1) == 0 and gqa.lib().gqa_cluster_capacity(17) == 0
+
+
 def test_kv_pool_bookkeeping(gqa):
     pool = gqa.KvPool(num_blocks=10, block_tokens=256, num_kv_heads=8, max_seqs=4,
                       max_blocks_per_seq=4)
