@@ -212,7 +212,7 @@ constexpr int kCombineGather = 1;  // ... and exchange the finished rows (KV-hea
 constexpr int kCombineSeqPar = 2;  // ... and merge with the other ranks' slices of the keys
 constexpr int kCombineRecord = 3;  // ... and leave the row's record instead of the output
 constexpr int kCombineWideGrid = 160;  // largest grid that runs with 4 lanes per channel
-constexpr int kCombineTile = 32;   // splits merged per pass
+constexpr int kCombineTile = 64;   // splits merged per pass
 constexpr int kCombineSlots = 8;   // partial sums per channel per pass, whatever the CTA width
 constexpr int kRecWords = kHeadDim + 2;  // a row's record: 128 channel sums, maximum, row sum
 
@@ -264,7 +264,11 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
     __shared__ float s_l[kCombineTile];
     __shared__ float s_part[kCombineSlots][kHeadDim];
     pdl_launch_dependents();
-    pdl_wait();
+    // The streaming kernel ahead of this one does not write the lengths. When the caller has
+    // promised that nothing else still running does either (early_prefetch), the work tables
+    // are built, and the address translation of this row's records warmed, while that kernel
+    // is still running: after the wait only the records themselves remain to be fetched.
+    if (!a.early_prefetch) pdl_wait();
     const WorkTables tables = build_work_tables(a, s_tables);
     // blockIdx.x = (sequence * q_tokens + token) * num_q_heads + head.
     const int32_t bt = blockIdx.x / a.num_q_heads;
@@ -282,6 +286,15 @@ __global__ void __launch_bounds__(kHeadDim * LANES)
         // raised the status word): nothing to read.
         if (threadIdx.x == 0) raise_status(a, kStatusBadInput);
         nsplits = 0;
+    }
+    if (a.early_prefetch) {
+        if (nsplits > 1 || (records && nsplits == 1)) {
+            const int64_t rec_floats = (int64_t)cols * (kHeadDim + 2);
+            for (int32_t s = threadIdx.x; s < nsplits; s += blockDim.x) {
+                prefetch_l2(a.workspace + (int64_t)(first + s) * rec_floats + col * kHeadDim);
+            }
+        }
+        pdl_wait();
     }
     // Not split: the streaming kernel already wrote the final output.
     if (MODE == kCombineLocal && nsplits <= 1) return;
