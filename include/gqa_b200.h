@@ -353,7 +353,9 @@ void gqa_session_destroy(gqa_session* s);
 /*
  * q_host/k_host/v_host/out_host: [batch, heads, head_dim] BF16 on the host. positions_host
  * [batch]: the new token's position per sequence; it attends positions 0..pos. Blocks until
- * out_host is filled. Cache pointers, layout and block table as in gqa_decode_params.
+ * out_host is filled. Buffers in pinned memory (cudaMallocHost / cudaHostRegister, mapped,
+ * 16-byte aligned) are read and written by the kernels where they lie; pageable ones go
+ * through the session's own pinned blocks. Cache pointers, layout and block table as in gqa_decode_params.
  */
 int gqa_session_step(gqa_session* s, int32_t batch, const void* q_host, const void* k_host,
                      const void* v_host, const void* qk_weight_dev, void* k_cache, void* v_cache,

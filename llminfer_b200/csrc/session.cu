@@ -141,6 +141,22 @@ void gqa_session_destroy(gqa_session* s) { release(s); }
 
 namespace {
 
+// Device address of a caller's host buffer when the kernels can use it where it lies (pinned,
+// mapped into this device, 16-byte aligned), else null. Asked every step: a buffer may have
+// been freed and its address handed out again as pageable memory since the last one.
+void* mapped_address(const void* host) {
+    void* device = nullptr;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+        attr.devicePointer != nullptr &&
+        (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15u) == 0) {
+        device = attr.devicePointer;
+    } else {
+        cudaGetLastError();  // a pageable pointer is not an error worth keeping
+    }
+    return device;
+}
+
 using Clock = std::chrono::steady_clock;
 
 int64_t ns_between(Clock::time_point a, Clock::time_point b) {
@@ -194,9 +210,20 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     const size_t off_v = off_k + kv_bytes(s, s->max_batch);
     const size_t off_len = off_v + kv_bytes(s, s->max_batch);
     const size_t off_pos = off_len + (size_t)s->max_batch * 4;
-    std::memcpy(s->host_in, q_host, qb);
-    std::memcpy(s->host_in + off_k, k_host, kb);
-    std::memcpy(s->host_in + off_v, v_host, kb);
+    // Rows the caller keeps in pinned memory are read where they lie; others are staged.
+    const uint8_t* q_in = nullptr;
+    const uint8_t* k_in = nullptr;
+    const uint8_t* v_in = nullptr;
+    uint8_t* out_direct = nullptr;
+    if (s->zero_copy) {
+        q_in = static_cast<const uint8_t*>(mapped_address(q_host));
+        k_in = static_cast<const uint8_t*>(mapped_address(k_host));
+        v_in = static_cast<const uint8_t*>(mapped_address(v_host));
+        out_direct = static_cast<uint8_t*>(mapped_address(out_host));
+    }
+    if (q_in == nullptr) std::memcpy(s->host_in, q_host, qb);
+    if (k_in == nullptr) std::memcpy(s->host_in + off_k, k_host, kb);
+    if (v_in == nullptr) std::memcpy(s->host_in + off_v, v_host, kb);
     int32_t* lens = reinterpret_cast<int32_t*>(s->host_in + off_len);
     int32_t* poss = reinterpret_cast<int32_t*>(s->host_in + off_pos);
     for (int32_t b = 0; b < batch; ++b) {
@@ -207,6 +234,9 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     const size_t used = off_pos + (size_t)batch * 4;
     // Pinned memory is mapped into the device's address space at the same address.
     const uint8_t* in = s->zero_copy ? s->host_in : s->dev_in;
+    if (q_in == nullptr) q_in = in;
+    if (k_in == nullptr) k_in = in + off_k;
+    if (v_in == nullptr) v_in = in + off_v;
     if (!s->zero_copy &&
         cudaMemcpyAsync(s->dev_in, s->host_in, used, cudaMemcpyHostToDevice, s->stream) !=
             cudaSuccess) {
@@ -220,8 +250,8 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     gqa_fused_front ff;
     std::memset(&ff, 0, sizeof(ff));
     if (s->fused_front) {
-        ff.k_new = in + off_k;
-        ff.v_new = in + off_v;
+        ff.k_new = k_in;
+        ff.v_new = v_in;
         ff.qk_weight = qk_weight_dev;
         ff.sin_cache = s->sin_table;
         ff.cos_cache = s->cos_table;
@@ -238,10 +268,10 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
         f.fixed_block = fixed_block;
         f.eps = 1e-6f;
         f.layout = *layout;
-        f.q = in;
+        f.q = q_in;
         f.q_out = s->dev_in;
-        f.k_new = in + off_k;
-        f.v_new = in + off_v;
+        f.k_new = k_in;
+        f.v_new = v_in;
         f.qk_weight = qk_weight_dev;
         f.sin_cache = s->sin_table;
         f.cos_cache = s->cos_table;
@@ -268,11 +298,11 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     p.blocks_per_seq = blocks_per_seq;
     p.fixed_block = fixed_block;
     p.layout = *layout;
-    p.q = s->fused_front ? static_cast<const void*>(in) : s->dev_in;
+    p.q = s->fused_front ? static_cast<const void*>(q_in) : s->dev_in;
     p.k_cache = k_cache;
     p.v_cache = v_cache;
     const bool out_to_host = s->zero_copy && comm == nullptr;
-    p.out = out_to_host ? s->host_out : s->dev_out;
+    p.out = out_to_host ? (out_direct != nullptr ? out_direct : s->host_out) : s->dev_out;
     p.workspace = s->workspace;
     p.workspace_bytes = s->workspace_bytes;
     p.seq_lens_host = lens;
@@ -305,7 +335,9 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
         // into the pinned block itself; NCCL gathers on the device and a copy follows. The
         // choice depends on the communicator and the size only, so every rank makes the same.
         const bool to_host = s->zero_copy && gqa_comm_peer_gather_fits(comm, qb) == 1;
-        rc = gqa_decode_sharded_fused(&p, front, comm, to_host ? s->host_gather : s->dev_gather);
+        uint8_t* gather_to = to_host ? (out_direct != nullptr ? out_direct : s->host_gather)
+                                     : s->dev_gather;
+        rc = gqa_decode_sharded_fused(&p, front, comm, gather_to);
         if (rc != GQA_OK) return rc;
         if (!to_host && cudaMemcpyAsync(s->host_gather, s->dev_gather, total,
                                         cudaMemcpyDeviceToHost, s->stream) != cudaSuccess) {
@@ -317,7 +349,7 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
         const Clock::time_point t_done = Clock::now();
         rc = status_code(s);
         if (rc != GQA_OK) return rc;
-        std::memcpy(out_host, s->host_gather, total);
+        if (!(to_host && out_direct != nullptr)) std::memcpy(out_host, s->host_gather, total);
         const Clock::time_point t_end = Clock::now();
         s->timing_ns[0] = ns_between(t_start, t_staged);
         s->timing_ns[1] = ns_between(t_staged, t_launched);
@@ -337,7 +369,7 @@ static int step_impl(gqa_session* s, gqa_comm* comm, int32_t batch, const void* 
     const Clock::time_point t_done = Clock::now();
     rc = status_code(s);
     if (rc != GQA_OK) return rc;
-    std::memcpy(out_host, s->host_out, qb);
+    if (!(out_to_host && out_direct != nullptr)) std::memcpy(out_host, s->host_out, qb);
     const Clock::time_point t_end = Clock::now();
     s->timing_ns[0] = ns_between(t_start, t_staged);
     s->timing_ns[1] = ns_between(t_staged, t_launched);

@@ -147,3 +147,15 @@ def test_session_step_from_host_buffers(gqa):
                                      max_seq_len=max_seq_len)
     abs_err, rel_err = H.errors(out_host[0].float().numpy(), want)
     assert abs_err <= 2e-2 and rel_err <= 2e-2, (abs_err, rel_err)
+    # Pageable host buffers go through the session's own pinned blocks instead of being used
+    # where they lie: same kernels, same bits (the cache row of `pos` is simply written again).
+    pageable = lambda bits: torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16)
+    out_paged = torch.zeros(1, hq, H.D, dtype=torch.bfloat16)
+    session = gqa.Session(1, hq, hkv, max_seq_len)
+    for _ in range(2):
+        session.step(pageable(q), pageable(k_new), pageable(v_new), H.bf16_tensor(w), dk, dv, layout,
+                     [pos], out_paged)
+    timing = session.last_timing()
+    session.close()
+    assert torch.equal(out_paged.view(torch.int16), out_host.view(torch.int16))
+    assert all(v >= 0 for v in timing.values()) and timing["wait_ns"] > 0
