@@ -509,10 +509,11 @@ int gqa_decode_seqpar(const gqa_decode_params* p, gqa_comm* comm);
  *     residual[b, n] = bf16(float(residual[b, n]) + sum_c attn_out[b, c] * weight[n, c])
  * Replaces kernel::fused_gemv_add_kernel_cu (code/source/op/kernel/cuda/matmul_kernel.cu:
  * 143-208; single token there, `batch` tokens here, the weights are read once for all of
- * them). FP32 accumulation on tensor cores; the summation order is fixed: per KV head eight
- * accumulators (one per block of 16 columns inside a query head) run over the KV head's query
- * heads in ascending order and are added in ascending order; KV heads are added in ascending
- * order; the residual comes last. Results agree with the reference kernel to one BF16 unit in
+ * them). FP32 accumulation on tensor cores; the summation order is fixed: the query heads of a
+ * KV head are taken in two halves when their number is even (else in one piece); per piece eight
+ * accumulators (one per block of 16 columns inside a query head) run over the piece's heads in
+ * ascending order and are added in ascending order; lower half + upper half; KV heads are added
+ * in ascending order; the residual comes last. Results agree with the reference kernel to one BF16 unit in
  * the last place. The weights travel by TMA: `weight` must stay valid and unchanged in place
  * (a tensor map per matrix is cached by address).
  *

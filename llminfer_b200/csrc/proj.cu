@@ -17,9 +17,11 @@
 // sit in shared memory as the B operand. A fragments come from the ring with ldmatrix.
 //
 // Summation order (fixed, so that a KV-head-parallel node reproduces the single-GPU result
-// bit for bit): per KV head eight FP32 accumulators, one per block of 16 columns inside a
-// query head, each running over the KV head's query heads in ascending order; the eight are
-// added in ascending order, KV heads are added in ascending order, then the residual.
+// bit for bit): a KV head with an even number of query heads is summed in two halves (lower
+// heads, upper heads), one with an odd number in one piece; per piece eight FP32 accumulators,
+// one per block of 16 columns inside a query head, each running over the piece's heads in
+// ascending order; the eight are added in ascending order, then lower + upper; KV heads are
+// added in ascending order, then the residual.
 //
 // A KV head's sum is stored in a small workspace as an 8-byte word that carries the sum and
 // the launch number (so no fence or atomic is needed), and in the sharded form pushed to
@@ -55,7 +57,7 @@ constexpr int kMaxHeadsPerGroup = 16;
 constexpr int kHeadTileBytes = kTileRows * kHeadDim * 2;  // 4 KiB: one head of one tile
 constexpr int kBoxBytes = kHeadTileBytes / 2;
 constexpr uint64_t kProjWaitNs = 2000000000ull;
-constexpr int kMaxSmem = 224 * 1024;  // leaves room for the static part
+constexpr int kMaxSmem = 220 * 1024;  // leaves room for the static part (about 4 KiB)
 
 struct OprojArgs {
     const __nv_bfloat16* x;    // [batch][heads * 128]
@@ -73,6 +75,7 @@ struct OprojArgs {
     int32_t heads;             // local query heads
     int32_t groups;            // local KV heads; the grid is a multiple of it
     int32_t stages;            // ring depth per warp
+    int32_t team;              // warps that share a task: 1, or 2 (each streams half the heads)
 };
 
 // Waits for a stage to fill; false when the time limit ran out. The clock is looked at only
@@ -119,16 +122,24 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
     __shared__ uint32_t s_local_step;
     __shared__ int s_timed_out;
     __shared__ float s_stage[kProjMaxWarps][kProjTokens * kTileRows];
+    __shared__ float s_team[kProjMaxWarps / 2][2][32 * 4];
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
     const int per_group = a.heads / a.groups;
     const int tiles = a.hidden / kTileRows;
-    // CTA c works on KV head c % groups; the warps of all CTAs of a KV head share its tiles.
+    // CTA c works on KV head c % groups; the teams of all CTAs of a KV head share its tiles.
+    // A team is one warp, or two warps that each stream half of the KV head's query heads.
     const int lg = blockIdx.x % a.groups;
-    const int worker = (blockIdx.x / a.groups) * nwarps + warp;
-    const int workers = (gridDim.x / a.groups) * nwarps;
+    const int team = a.team;
+    const int member = warp % team;
+    const int unit = warp / team;
+    const int units = nwarps / team;
+    const int worker = (blockIdx.x / a.groups) * units + unit;
+    const int workers = (gridDim.x / a.groups) * units;
+    const int team_heads = per_group / team;
+    const int head0 = member * team_heads;
     const int x_pitch = per_group * kHeadDim * 2 + 16;  // bytes per token row
     const uint32_t ring = smem_u32(s_dyn) + warp * a.stages * kHeadTileBytes;
     uint8_t* s_x = s_dyn + nwarps * a.stages * kHeadTileBytes;
@@ -136,7 +147,7 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
 
     // ---- producer side: the warp's sequence of (tile, head) stages ------------------------
     const uint64_t policy = l2_policy_evict_first();
-    int prod_tile = worker, prod_head = 0, prod_stage = 0;
+    int prod_tile = worker, prod_head = head0, prod_stage = 0;
     auto issue = [&]() {
         if (prod_tile >= tiles) return;
         if (lane == 0) {
@@ -150,8 +161,8 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
             tma_load_2d(dst + kBoxBytes, &wmap, bar, col + 64, prod_tile * kTileRows, policy);
         }
         if (++prod_stage == a.stages) prod_stage = 0;
-        if (++prod_head == per_group) {
-            prod_head = 0;
+        if (++prod_head == head0 + team_heads) {
+            prod_head = head0;
             prod_tile += workers;
         }
     };
@@ -209,11 +220,13 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
     int cons_stage = 0;
     uint32_t cons_parity = 0;
     bool timed_out = false;
+    uint32_t task = 0;  // tasks this team has finished (selects the team's exchange buffer)
 #pragma unroll 1
-    for (int tile = worker; tile < tiles && !timed_out; tile += workers) {
+    for (int tile = worker; tile < tiles; tile += workers, ++task) {
         // One accumulator per block of 16 columns of a head (eight independent MMA chains, so
-        // that the tensor pipe's latency is not paid per instruction); each runs over the KV
-        // head's query heads in ascending order.
+        // that the tensor pipe's latency is not paid per instruction); each runs over this
+        // warp's heads of the KV head in ascending order. A warp whose wait ran out stops
+        // reading but stays in step with its team (the barrier below has no time limit).
         float part[8][4];
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -221,12 +234,10 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
             for (int i = 0; i < 4; ++i) part[ks][i] = 0.f;
         }
 #pragma unroll 1
-        for (int head = 0; head < per_group; ++head) {
+        for (int head = head0; head < head0 + team_heads; ++head) {
             const uint32_t tile_addr = ring + cons_stage * kHeadTileBytes + w_row_off;
-            if (!wait_full(bars + cons_stage * 8, cons_parity)) {
-                timed_out = true;
-                break;
-            }
+            if (!timed_out && !wait_full(bars + cons_stage * 8, cons_parity)) timed_out = true;
+            if (timed_out) continue;
             const uint32_t x_addr = x_lane + head * (kHeadDim * 2);
 #pragma unroll
             for (int kp = 0; kp < 4; ++kp) {  // 32 columns per pass, ascending
@@ -246,7 +257,6 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
             __syncwarp();
             issue();  // the stage is free again
         }
-        if (timed_out) break;
         // The eight block sums, added in ascending order.
         float acc[4];
 #pragma unroll
@@ -254,6 +264,24 @@ __global__ void __launch_bounds__(kProjMaxWarps * 32, 3)
             acc[i] = part[0][i];
 #pragma unroll
             for (int ks = 1; ks < 8; ++ks) acc[i] += part[ks][i];
+        }
+        if (team == 2) {
+            // The warp of the upper heads hands its sums to the warp of the lower heads, which
+            // adds them (lower + upper) and carries the task on. Two buffers taken in turn: the
+            // upper warp cannot be two tasks ahead of a barrier the lower one has not passed.
+            float* hand = s_team[unit][task & 1u] + lane * 4;
+            if (member == 1) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) hand[i] = acc[i];
+            }
+            if (unit == 0) {
+                asm volatile("bar.sync 1, 64;" ::: "memory");
+            } else {
+                asm volatile("bar.sync 2, 64;" ::: "memory");
+            }
+            if (member == 1) continue;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[i] += hand[i];
         }
         // acc[0..1]: row gid, tokens 2 tig and 2 tig + 1; acc[2..3]: row gid + 8. With a single
         // KV head in the whole model that is the result; otherwise each sum becomes a tagged
@@ -480,19 +508,32 @@ int run(const gqa_oproj_params* p, const SplitOut* split, gqa_comm* comm) {
         if (oe != cudaSuccess || fit < 1) return GQA_ERR_CUDA;
         if (ctas_per_sm > fit) ctas_per_sm = fit;
     }
-    // Every warp gets the same number of tiles (k) of its KV head, or one fewer: as many
-    // warps as the GPU holds at once, but no more than tiles; small problems use narrower
+    // A task (16-row tile, KV head) belongs to a team: one warp, or - when the KV head has an
+    // even number of query heads - two warps of a CTA that each stream half of them and add
+    // their sums. With single warps the Qwen3-32B projection has 2560 tasks for 1776 warp
+    // slots: 1280 warps take two each and a third of the slots stay empty, so the SMs that got
+    // three CTAs stream half as much again as those that got two and the launch ends with
+    // them. Teams of two make it 888 slots of three tasks each.
+    static const bool teams_off = [] {
+        const char* v = std::getenv("GQA_OPROJ_TEAM");
+        return v != nullptr && v[0] == '1';
+    }();
+    const int team = (!teams_off && per_group >= 2 && per_group % 2 == 0) ? 2 : 1;
+    const int units_max = kProjMaxWarps / team;  // teams per CTA
+    // Every team gets the same number of tiles (k) of its KV head, or one fewer: as many
+    // teams as the GPU holds at once, but no more than tiles; small problems use narrower
     // CTAs so that they still reach every SM.
     int ctas_per_group = ctas_per_sm * sms / groups;
     if (ctas_per_group < 1) ctas_per_group = 1;
-    const int k = (tiles + ctas_per_group * kProjMaxWarps - 1) / (ctas_per_group * kProjMaxWarps);
-    const int workers = (tiles + k - 1) / k;  // per KV head
+    const int k = (tiles + ctas_per_group * units_max - 1) / (ctas_per_group * units_max);
+    const int workers = (tiles + k - 1) / k;  // teams per KV head
     int warps = kProjMaxWarps;
-    if ((int64_t)workers * groups < (int64_t)sms * kProjMaxWarps) {
-        warps = (int)((int64_t)workers * groups / sms);
-        if (warps < 1) warps = 1;
+    if ((int64_t)workers * groups * team < (int64_t)sms * kProjMaxWarps) {
+        warps = (int)((int64_t)workers * groups * team / sms) / team * team;
+        if (warps < team) warps = team;
     }
-    const int grid = (workers + warps - 1) / warps * groups;
+    const int units = warps / team;
+    const int grid = (workers + units - 1) / units * groups;
     const size_t smem = smem_bytes(warps, stages, per_group);
     if (smem > (size_t)kMaxSmem) return GQA_ERR_SHAPE;
     CUtensorMap wmap;
@@ -525,6 +566,7 @@ int run(const gqa_oproj_params* p, const SplitOut* split, gqa_comm* comm) {
         a.heads = p->num_q_heads;
         a.groups = groups;
         a.stages = stages;
+        a.team = team;
         PeerGatherArgs g;
         std::memset(&g, 0, sizeof(g));
         cudaError_t e;
