@@ -1,12 +1,15 @@
 """Sequence-parallel decode on a single GPU: with one rank the merge across ranks has one
 record to merge, so gqa_decode_seqpar must reproduce gqa_decode bit for bit, through the same
 kernels a multi-GPU run uses (every unit leaves a partial record, the combine kernel's
-cross-rank mode, the peer window)."""
+cross-rank mode, the peer window), and both must agree with the FP64 oracle. The merge of
+several ranks' records (empty ones included) is checked against the oracle on one GPU in
+test_gpu_partial_merge.py and across real ranks in multi_gpu_worker.py."""
 import numpy as np
 import pytest
 import torch
 
 import helpers as H
+from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -39,11 +42,12 @@ def test_one_rank_reproduces_decode(gqa, comm, hq, hkv, lens, split_keys):
     batch, block_tokens, d = len(lens), 256, 128
     blocks_per_seq = max(-(-n // block_tokens) for n in lens)
     num_blocks = batch * blocks_per_seq
-    table = torch.from_numpy(rng.permutation(num_blocks).reshape(batch, blocks_per_seq)
-                             .astype(np.int32)).to("cuda:0")
-    q = H.bf16_tensor(H.rand_bits(rng, (batch, hq, d)))
-    k = H.bf16_tensor(H.rand_bits(rng, (num_blocks, hkv, block_tokens, d)))
-    v = H.bf16_tensor(H.rand_bits(rng, (num_blocks, hkv, block_tokens, d)))
+    table_np = rng.permutation(num_blocks).reshape(batch, blocks_per_seq).astype(np.int32)
+    table = torch.from_numpy(table_np).to("cuda:0")
+    q_bits = H.rand_bits(rng, (batch, hq, d))
+    k_bits = H.rand_bits(rng, (num_blocks, hkv, block_tokens, d))
+    v_bits = H.rand_bits(rng, (num_blocks, hkv, block_tokens, d))
+    q, k, v = H.bf16_tensor(q_bits), H.bf16_tensor(k_bits), H.bf16_tensor(v_bits)
     layout = gqa.layout_pool(num_blocks, block_tokens, hkv)
     ws = gqa.binding.workspace_for(batch, hq, hkv, "cuda:0")
     status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
@@ -58,3 +62,9 @@ def test_one_rank_reproduces_decode(gqa, comm, hq, hkv, lens, split_keys):
         torch.cuda.synchronize()
         assert int(status.item()) == 0
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    ref = oracle.gqa_decode(q_bits, k_bits.reshape(-1), v_bits.reshape(-1), lens, hkv=hkv,
+                            stride_block=layout.stride_block, stride_token=layout.stride_token,
+                            stride_head=layout.stride_head, block_tokens=block_tokens,
+                            block_table=table_np)
+    abs_err, rel_err = H.errors(H.f32_of(got), ref)
+    assert abs_err <= 2e-2 and rel_err <= 1e-2, (abs_err, rel_err)
