@@ -82,10 +82,12 @@ def test_fused_equals_front_then_decode_reference_layout(gqa, hq, hkv, length, s
         assert torch.equal(k_b.view(torch.int16)[1, length:], H.bf16_tensor(k0).view(torch.int16)[1, length:])
 
 
-@pytest.mark.parametrize("tokens", [1, 2, 4])
-def test_fused_paged_ragged_batch(gqa, tokens):
-    rng = np.random.default_rng(91 + tokens)
-    batch, hq, hkv, block_tokens = 6, 32, 8, 256
+@pytest.mark.parametrize("tokens,hq", [(1, 32), (2, 32), (4, 32), (4, 64), (8, 64)])
+def test_fused_paged_ragged_batch(gqa, tokens, hq):
+    """(4, 64) and (8, 64) have 32 and 64 (token, head) columns per unit: two and four passes
+    over the cache, each appending its own tokens' rows before the next one reads them."""
+    rng = np.random.default_rng(91 + tokens + hq)
+    batch, hkv, block_tokens = 6, 8, 256
     lens = [tokens, 256, 257 + tokens, 1024, 1999, 700]
     blocks_per_seq = 8
     num_blocks = batch * blocks_per_seq
