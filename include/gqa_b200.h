@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define GQA_B200_ABI_VERSION 2
+#define GQA_B200_ABI_VERSION 3
 
 /* ---- status codes ------------------------------------------------------------------- */
 #define GQA_OK 0
@@ -120,10 +120,16 @@ int gqa_layout_pool(int32_t num_blocks, int32_t block_tokens, int32_t num_kv_hea
  *                   layer_id) and batch must be 1.
  *   workspace       FP32 scratch for split partials, gqa_decode_plan() gives the size; may
  *                   be null when the plan needs no split. Contents need no initialisation.
- *   split_keys      0 = choose from lengths and SM count; otherwise keys per split
- *                   (rounded up to a multiple of GQA_CHUNK_KEYS). The value of a head's
+ *   split_keys      0 = choose from lengths and SM count (uniform splits, splits merged inside
+ *                   thread-block clusters, or an even cut of all units over the CTAs, see
+ *                   gqa_decode_plan_info); otherwise keys per split (rounded up to a multiple
+ *                   of GQA_CHUNK_KEYS). With a non-zero split_keys the value of a head's
  *                   output depends on (length, split_keys) only, never on batch size, head
- *                   count or rank count, so equal split_keys give bit-equal results.
+ *                   count or rank count, so equal split_keys give bit-equal results; with 0
+ *                   the summation order may depend on all of those. GQA_SPLIT_EVEN asks for
+ *                   the even cut whatever the planner would choose (BF16 gqa_decode,
+ *                   gqa_decode_fused and the sharded gathers; GQA_ERR_UNSUPPORTED elsewhere,
+ *                   GQA_ERR_WORKSPACE when the scratch cannot hold num_ctas + units records).
  *   max_ctas        0 = one CTA per SM; otherwise an upper bound on the grid.
  *   early_prefetch  0 = start reading the cache only when all earlier work of the stream has
  *                   finished. 1 = the caller promises that work still running ahead of this
@@ -137,6 +143,8 @@ int gqa_layout_pool(int32_t num_blocks, int32_t block_tokens, int32_t num_kv_hea
  *                   met out-of-range device-side input.
  *   stream          cudaStream_t (null = default stream), as the reference passes it.
  */
+#define GQA_SPLIT_EVEN (-1)  /* gqa_decode_params.split_keys: cut all units evenly over the CTAs */
+
 typedef struct gqa_decode_params {
     int32_t dtype;
     int32_t batch;
@@ -175,6 +183,13 @@ typedef struct gqa_decode_plan_info {
                                  per split) instead: no combine launch and no workspace, provided
                                  the GPU holds all clusters at once and no gather is fused in */
     size_t workspace_bytes;   /* scratch the chosen plan needs */
+    int32_t even_cut;         /* 1: no uniform splits; the stages of all (sequence, kv head) units
+                                 form one flat sequence that is cut evenly over num_ctas CTAs, a
+                                 partial record per piece of a cut unit (num_items = num_ctas +
+                                 units records at most), merged by the combine launch. The cut
+                                 follows the lengths the kernels read. split_chunks is then the
+                                 granularity of the cut, max_splits the most pieces of a unit */
+    int32_t reserved;
 } gqa_decode_plan_info;
 
 /*

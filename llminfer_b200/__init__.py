@@ -6,6 +6,7 @@ is the thin binding used by the tests and the benchmark; it has no CPU fallback.
 """
 from .binding import (  # noqa: F401
     FusedFront,
+    SPLIT_EVEN,
     GqaError,
     KvLayout,
     KvPool,

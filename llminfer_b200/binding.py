@@ -66,6 +66,9 @@ class _DecodeParams(C.Structure):
     ]
 
 
+SPLIT_EVEN = -1  # split_keys value: cut all units evenly over the CTAs (GQA_SPLIT_EVEN)
+
+
 class _PlanInfo(C.Structure):
     _fields_ = [
         ("split_chunks", C.c_int32),
@@ -75,6 +78,8 @@ class _PlanInfo(C.Structure):
         ("needs_combine", C.c_int32),
         ("cluster_size", C.c_int32),
         ("workspace_bytes", C.c_size_t),
+        ("even_cut", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 

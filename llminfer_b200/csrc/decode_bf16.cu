@@ -83,7 +83,7 @@ __device__ __forceinline__ bool wait_stage(uint32_t bar, uint32_t parity) {
 }
 
 struct Cursor {
-    int32_t item;
+    int32_t next;   // position of the item after the current one
     int32_t k;
     int32_t k_end;
     int32_t k_new;  // first stage that holds a position of the new tokens
@@ -139,14 +139,25 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     const WorkTables tables = build_work_tables(a, s_tables);
     __syncthreads();
 
-    // Persistent grid: items blockIdx.x, blockIdx.x + gridDim.x, ... Cluster launch: the one
-    // item this CTA's place in its cluster stands for (or none).
+    // The CTA's work is a walk over positions [pos_begin, pos_end). Persistent grid: items
+    // blockIdx.x, blockIdx.x + gridDim.x, ... Even cut: this CTA's share of the flat sequence
+    // of cells, one piece per unit it touches. Cluster launch: the one item this CTA's place
+    // in its cluster stands for (or none).
     Item own = {};
     const bool has_own = CLUSTER ? cluster_item(a, tables, &own) : false;
-    const int32_t n_items = CLUSTER ? (has_own ? (int32_t)blockIdx.x + 1 : 0) : total_items(a, tables);
-    auto item_of = [&](int32_t idx) -> Item {
-        if (CLUSTER) return own;
-        return decode_item(a, tables, idx);
+    const bool even = !CLUSTER && a.even_ctas > 0;
+    int32_t pos_begin = 0, pos_end = has_own ? 1 : 0;
+    if (!CLUSTER) {
+        const int32_t total = total_items(a, tables);
+        const int32_t ctas = even_ctas(a, total);
+        pos_begin = even ? even_begin(blockIdx.x, total, ctas) : (int32_t)blockIdx.x;
+        pos_end = even ? even_begin(blockIdx.x + 1, total, ctas) : total;
+    }
+    // The item at a position, the index of its partial record and the position after it.
+    auto fetch = [&](int32_t pos) -> Step {
+        if (CLUSTER) return Step{own, 0, pos_end, true};
+        if (even) return even_piece(a, tables, pos, pos_end, blockIdx.x);
+        return Step{decode_item(a, tables, pos), pos, pos + (int32_t)gridDim.x, true};
     };
     const int32_t group = a.group;
     const int32_t q_tokens = a.q_tokens;
@@ -157,7 +168,7 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
 
     // ---- producer side: this warp's stage sequence across the CTA's items ----------------
     Cursor prod;
-    prod.item = blockIdx.x - gridDim.x;
+    prod.next = pos_begin;
     prod.k = 0;
     prod.k_end = 0;
     prod.k_new = 0;
@@ -166,11 +177,16 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     prod.valid = true;
     auto normalize = [&](Cursor& c) {
         while (c.valid && c.k >= c.k_end) {
-            c.item += gridDim.x;
-            if (c.item >= n_items) {
+            if (c.next >= pos_end) {
                 c.valid = false;
             } else {
-                const Item it = item_of(c.item);
+                const Step st = fetch(c.next);
+                const Item& it = st.it;
+                c.next = st.next;
+                if (!st.valid) {
+                    c.valid = false;
+                    break;
+                }
                 c.b = it.b;
                 c.hk = it.hk;
                 c.k = it.chunk_begin * kChunkKeys / KEYS + warp;
@@ -237,8 +253,12 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
     bool dead = false;
 
 #pragma unroll 1
-    for (int32_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-        const Item it = item_of(item);
+    for (int32_t pos = pos_begin, pos_next = 0; pos < pos_end; pos = pos_next) {
+        const Step step = fetch(pos);
+        if (!step.valid) break;
+        const Item& it = step.it;
+        const int32_t record = step.record;
+        pos_next = step.next;
         const int32_t new_lo = it.len - q_tokens;  // position of the first query token
 
         // Row of column c in q / out: [sequence][token][query head][channel].
@@ -557,9 +577,9 @@ gqa_decode_stream_bf16(const __grid_constant__ CUtensorMap tmap_k,
             const bool final_out = (it.nsplits == 1) && a.always_partial == 0;
             // A record that does not fit the scratch is not written (lengths read from the
             // device may have outgrown what the scratch was sized for).
-            const bool fits = CLUSTER || final_out || item < a.item_capacity;
+            const bool fits = CLUSTER || final_out || record < a.item_capacity;
             if (!fits && threadIdx.x == 0) raise_status(a, kStatusBadInput);
-            float* rec = CLUSTER ? s_rec : a.workspace + (int64_t)item * cols * (kHeadDim + 2);
+            float* rec = CLUSTER ? s_rec : a.workspace + (int64_t)record * cols * (kHeadDim + 2);
             __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
             for (int idx = threadIdx.x; fits && idx < cols * kHeadDim; idx += WARPS * 32) {
                 const int n = idx >> 7;

@@ -76,7 +76,7 @@ int validate_decode(const gqa_decode_params* p, bool allow_empty = false, bool i
         return GQA_ERR_ALIGN;
     }
     if (p->seq_lens_host == nullptr && p->seq_lens_dev == nullptr) return GQA_ERR_NULL;
-    if (p->split_keys < 0 || p->max_ctas < 0 || p->plan_len_hint < 0) return GQA_ERR_RANGE;
+    if (p->split_keys < GQA_SPLIT_EVEN || p->max_ctas < 0 || p->plan_len_hint < 0) return GQA_ERR_RANGE;
     int64_t capacity;  // tokens one sequence can hold
     if (p->block_table_dev != nullptr) {
         if (p->blocks_per_seq <= 0) return GQA_ERR_SHAPE;
@@ -132,6 +132,18 @@ constexpr double kItemOverhead = 1.0;
 constexpr double kCombineBase = 3.0;
 constexpr double kCombinePerSplit = 0.05;
 constexpr double kClusterMerge = 1.0;  // cluster barrier + merge through distributed shared memory
+constexpr double kEvenMargin = 0.5;    // the even cut has to beat the best split by this much
+
+// Stages that starting on a unit costs a CTA in the even cut (merge of the previous piece's
+// warps, the new unit's query rows): every unit counts for that many stages more than it has.
+int32_t even_pad_cells() {
+    static const int32_t pad = [] {
+        const char* v = std::getenv("GQA_EVEN_PAD");
+        const int n = v != nullptr ? std::atoi(v) : 8;
+        return n < 0 ? 0 : (n > 64 ? 64 : n);
+    }();
+    return pad;
+}
 
 struct PlanInput {
     int32_t batch;
@@ -148,6 +160,10 @@ struct PlanInput {
     // Splits merged inside thread-block clusters (one cluster per unit, one CTA per split):
     const int32_t* cluster_fit;  // [17] clusters of each size the GPU holds at once; null = never
     int32_t cluster_chunks;      // chunks of the longest sequence the kernels may ever see
+    // Even cut of all units' stages over the CTAs (BF16 streaming kernel, planner's choice only):
+    bool allow_even;
+    bool force_even;             // the caller asked for it: no cost comparison
+    int32_t capacity_chunks;     // chunks a sequence can hold
 };
 
 constexpr int kMaxClusterSize = 16;  // 8 is the portable limit; up to 16 where the GPU takes it
@@ -205,6 +221,7 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
         out->num_ctas = (int32_t)(items < g_max ? (items > 0 ? items : 1) : g_max);
         out->needs_combine = ms > 1 ? 1 : 0;
         out->cluster_size = ms > 1 ? cluster_for(q) : 0;
+        out->even_cut = 0;
         out->workspace_bytes = ms > 1 ? (size_t)items * rec : 0;
         if (in.workspace_bytes != 0 && out->workspace_bytes > in.workspace_bytes) {
             return GQA_ERR_WORKSPACE;
@@ -242,8 +259,70 @@ int make_plan(const PlanInput& in, gqa_decode_plan_info* out) {
         }
         if (items > (int64_t)8 * g_max) break;
     }
+    // The even cut: every CTA streams the same number of stages (cells of chunk_align chunks),
+    // pieces of cut units are merged by the combine launch, G + U records. Only for lengths
+    // that differ by more than a quarter: with equal lengths uniform splits already fill the
+    // GPU evenly and measure a little faster (fewer CTAs change units at the same moment).
+    bool ragged = false;
+    if (in.lens != nullptr) {
+        int32_t lo = INT32_MAX, hi = 0;
+        for (int32_t b = 0; b < in.batch; ++b) {
+            if (in.lens[b] <= 0) continue;
+            lo = in.lens[b] < lo ? in.lens[b] : lo;
+            hi = in.lens[b] > hi ? in.lens[b] : hi;
+        }
+        ragged = hi > 0 && (int64_t)4 * hi > (int64_t)5 * lo;
+    }
+    if (in.allow_even && (ragged || in.force_even)) {
+        const int32_t pad = even_pad_cells();
+        int64_t total = 0;
+        for (int32_t b = 0; b < in.batch; ++b) {
+            const int32_t len = in.lens ? in.lens[b] : in.uniform_len;
+            const int32_t cells = ceil_div(ceil_div(len, kChunkKeys), in.chunk_align);
+            total += (int64_t)(cells > 0 ? cells + pad : 0) * in.num_kv_heads;
+            if (!in.lens) {
+                total *= in.batch;
+                break;
+            }
+        }
+        const int64_t cap_total = units * (ceil_div(in.capacity_chunks, in.chunk_align) + pad);
+        int64_t ctas = (total + kPlanWarps - 1) / kPlanWarps;  // at least one stage per warp
+        ctas = ctas < 1 ? 1 : (ctas > g_max ? g_max : ctas);
+        const int64_t per_cta = (total + ctas - 1) / ctas;
+        // A unit's start is paid for by its padding; a range that starts inside a unit is not.
+        const double cost =
+            (double)((per_cta + kPlanWarps - 1) / kPlanWarps) * in.chunk_align +
+            in.overhead_scale * (kItemOverhead + kCombineBase +
+                                 kCombinePerSplit * ((double)ctas / (double)units + 1.0));
+        const size_t ws = (size_t)(ctas + units) * rec;
+        const bool fits = in.workspace_bytes == 0 || ws <= in.workspace_bytes;
+        if (in.force_even && !fits) return GQA_ERR_WORKSPACE;
+        if (cap_total < (1 << 30) && ctas + units < INT32_MAX && fits &&
+            (in.force_even || !have || cost < best_cost - kEvenMargin)) {
+            out->split_chunks = in.chunk_align;
+            const int64_t widest = ((int64_t)ceil_div(max_chunks, in.chunk_align) + per_cta - 1) / per_cta + 1;
+            out->max_splits = (int32_t)(widest < ctas ? widest : ctas);
+            out->num_items = (int32_t)(ctas + units);
+            out->num_ctas = (int32_t)ctas;
+            out->needs_combine = 1;
+            out->cluster_size = 0;
+            out->even_cut = 1;
+            out->workspace_bytes = ws;
+            return GQA_OK;
+        }
+    }
+    if (in.force_even) return GQA_ERR_UNSUPPORTED;  // more cells than the cut can index
     if (!have) return GQA_ERR_WORKSPACE;
     return finish(best_q);
+}
+
+// GQA_EVEN_CUT=0 keeps the planner to uniform splits (for measurements).
+bool even_cut_disabled() {
+    static const bool off = [] {
+        const char* v = std::getenv("GQA_EVEN_CUT");
+        return v != nullptr && v[0] == '0';
+    }();
+    return off;
 }
 
 // GQA_CLUSTER_MERGE=0 keeps the combine launch for every split plan (for measurements).
@@ -292,10 +371,11 @@ const int32_t* cluster_fit_table(int32_t sm_count) {
 }
 
 int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out,
-                     bool allow_cluster = true);
+                     bool allow_cluster = true, bool allow_even = true);
 
 int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_plan_info* out,
-                     bool allow_cluster) {
+                     bool allow_cluster, bool allow_even) {
+    std::memset(out, 0, sizeof(*out));
     PlanInput in;
     in.batch = p->batch;
     in.num_kv_heads = p->num_kv_heads;
@@ -308,7 +388,8 @@ int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pl
     }
     in.sm_count = sm_count * (p->dtype == GQA_DTYPE_BF16 ? stream_shape().ctas_per_sm : 1);
     in.max_ctas = p->max_ctas;
-    in.split_keys = p->split_keys;
+    const bool force_even = p->split_keys == GQA_SPLIT_EVEN;
+    in.split_keys = force_even ? 0 : p->split_keys;
     in.workspace_bytes = p->workspace != nullptr ? p->workspace_bytes : 0;
     const int32_t stage_keys = p->dtype == GQA_DTYPE_BF16 ? stream_shape().keys : kChunkKeys;
     in.chunk_align = stage_keys > kChunkKeys ? stage_keys / kChunkKeys : 1;
@@ -326,6 +407,11 @@ int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pl
         p->layout.block_tokens % stage_keys != 0) {
         return GQA_ERR_SHAPE;
     }
+    if (force_even && !(allow_even && p->dtype == GQA_DTYPE_BF16)) return GQA_ERR_UNSUPPORTED;
+    in.force_even = force_even;
+    in.allow_even = force_even || (allow_even && p->dtype == GQA_DTYPE_BF16 &&
+                                   p->split_keys == 0 && !even_cut_disabled());
+    in.capacity_chunks = ceil_div((int32_t)capacity, kChunkKeys);
     const int32_t g_max = in.max_ctas > 0 && in.max_ctas < in.sm_count ? in.max_ctas : in.sm_count;
     if (p->seq_lens_host != nullptr || p->seq_lens_dev == nullptr) {
         int rc = make_plan(in, out);
@@ -344,7 +430,17 @@ int plan_from_params(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pl
     hint.workspace_bytes = 0;
     int rc = make_plan(hint, out);
     if (rc != GQA_OK) return rc;
+    if (out->even_cut) {
+        // The even cut follows the device lengths by itself and its scratch does not depend on
+        // them; if the caller's scratch cannot hold it, fall back to uniform splits.
+        if (in.workspace_bytes == 0 || out->workspace_bytes <= in.workspace_bytes) return GQA_OK;
+        if (force_even) return GQA_ERR_WORKSPACE;
+        hint.allow_even = false;
+        rc = make_plan(hint, out);
+        if (rc != GQA_OK) return rc;
+    }
     PlanInput full = in;
+    full.allow_even = false;
     full.uniform_len = (int32_t)capacity;
     int32_t chunks = out->split_chunks;
     const int32_t cap_chunks = ceil_div((int32_t)capacity, kChunkKeys);
@@ -599,12 +695,13 @@ int gqa_decode_plan(const gqa_decode_params* p, int32_t sm_count, gqa_decode_pla
     const int32_t per_pass = kMaxColumns / (p->num_q_heads / p->num_kv_heads);
     if (tokens_of(p) > per_pass) planned.q_tokens = per_pass;
     rc = plan_from_params(&planned, sm_count, out);
-    if (rc == GQA_OK && out->cluster_size > 0) {
-        // gqa_decode merges these splits inside clusters and needs no workspace; the calls that
-        // cannot (gathers, records) cut the keys as if clusters did not exist: report the
-        // larger of the two workspaces so that one allocation serves them all.
+    if (rc == GQA_OK && (out->cluster_size > 0 || out->even_cut)) {
+        // gqa_decode merges these splits inside clusters and needs no workspace, or cuts the
+        // units evenly over the CTAs; the calls that cannot (gathers, records) cut the keys in
+        // uniform splits: report the larger of the two workspaces so that one allocation
+        // serves them all.
         gqa_decode_plan_info plain;
-        if (plan_from_params(&planned, sm_count, &plain, false) == GQA_OK &&
+        if (plan_from_params(&planned, sm_count, &plain, false, false) == GQA_OK &&
             plain.workspace_bytes > out->workspace_bytes) {
             out->workspace_bytes = plain.workspace_bytes;
         }
@@ -709,7 +806,8 @@ int decode_impl(const gqa_decode_params* p, const gqa_fused_front* front,
         planned.q_tokens = tokens;
         // Splits can be merged inside thread-block clusters (no scratch, no second launch)
         // unless the merged rows have to leave through a gather or as records.
-        rc = plan_from_params(&planned, sms, &plan, mode == DecodeMode::kOutput && gather == nullptr);
+        rc = plan_from_params(&planned, sms, &plan, mode == DecodeMode::kOutput && gather == nullptr,
+                              mode == DecodeMode::kOutput);
     }
     if (rc != GQA_OK) return rc;
     const int32_t group = p->num_q_heads / p->num_kv_heads;
@@ -769,6 +867,8 @@ int decode_impl(const gqa_decode_params* p, const gqa_fused_front* front,
     a.item_capacity = fit > (size_t)INT32_MAX ? INT32_MAX : (int32_t)fit;
     a.num_blocks = p->layout.num_blocks;
     a.cluster_size = cluster;
+    a.even_ctas = plan.even_cut ? plan.num_ctas : 0;
+    a.even_pad = plan.even_cut ? even_pad_cells() : 0;
     a.scale_log2 = (1.0f / sqrtf((float)kHeadDim)) * 1.44269504088896340736f;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(p->stream);
 

@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol(gqa):
     for name in sorted(declared):
         assert hasattr(handle, name), f"{name} is declared in the header but not exported"
     assert declared == set(gqa.binding.exported_symbols())
-    assert handle.gqa_abi_version() == 2
+    assert handle.gqa_abi_version() == 3
     assert gqa.status_string(0) == "ok"
     assert "workspace" in gqa.status_string(-6)
 
@@ -67,7 +67,7 @@ def test_validation_codes(gqa):
         "block_out_of_range": dict(fixed_block=1),
         "batch_needs_table": dict(batch=2, seq_lens=[5, 5]),
         "ragged_needs_device_lens": dict(batch=2, seq_lens=[5, 6], paged=True, blocks_per_seq=1),
-        "negative_split": dict(split_keys=-1),
+        "negative_split": dict(split_keys=-2),
     }.items():
         with pytest.raises(gqa.GqaError) as e:
             plan(gqa, **kw)
@@ -177,13 +177,48 @@ def test_planner_fills_the_gpu_at_long_context(gqa):
                             device_lens=True)
         chunks = length // 32
         assert p["needs_combine"] == 1
+        fair = batch * 8 * chunks / 148
+        assert p["even_cut"] == 0  # equal lengths: uniform splits
         assert p["num_ctas"] >= 128 or p["num_items"] < 148
         rounds = -(-p["num_items"] // 148)
         # No CTA works on more than ~6% above its fair share of the chunks.
         per_cta = rounds * p["split_chunks"]
-        fair = batch * 8 * chunks / 148
         assert per_cta <= max(1.10 * fair + 4, 8), (length, p)
         assert p["workspace_bytes"] == p["num_items"] * (hq // 8) * 130 * 4
+    assert p["cluster_size"] > 0  # 1K: merged inside clusters
+
+
+def test_planner_cuts_ragged_batches_evenly(gqa):
+    """Lengths that differ: uniform splits leave some CTAs with far more keys than others; the
+    even cut gives every CTA the same number of stages and needs num_ctas + units records
+    whatever the lengths are. An explicit split size, a scratch that cannot hold those records,
+    equal lengths and lengths known on the device only keep uniform splits."""
+    lens = [7041, 4359, 4800, 4966, 5665, 4013, 2459, 3116, 4044, 6423, 4328, 6447, 630, 7337,
+            4651, 4958]
+    layout = gqa.layout_pool(16 * 32, 256, 8)
+    kw = dict(dtype=2, batch=16, num_q_heads=32, num_kv_heads=8, layout=layout, seq_lens=lens,
+              paged=True, blocks_per_seq=32, device_lens=True)
+    p = gqa.decode_plan(**kw)
+    rec = 4 * 130 * 4
+    assert p["even_cut"] == 1 and p["num_ctas"] == 148 and p["needs_combine"] == 1
+    assert p["split_chunks"] == 2 and p["num_items"] == 148 + 128 and p["cluster_size"] == 0
+    assert p["workspace_bytes"] >= p["num_items"] * rec
+    assert gqa.decode_plan(split_keys=2048, **kw)["even_cut"] == 0
+    tight = gqa.decode_plan(workspace_bytes=200 * rec, **kw)
+    assert tight["even_cut"] == 0 and tight["workspace_bytes"] <= 200 * rec
+    assert gqa.decode_plan(**dict(kw, seq_lens=[4096] * 16))["even_cut"] == 0  # equal lengths
+    asked = gqa.decode_plan(**dict(kw, seq_lens=[4096] * 16, split_keys=gqa.SPLIT_EVEN))
+    assert asked["even_cut"] == 1 and asked["num_items"] == 148 + 128
+    with pytest.raises(gqa.GqaError) as e:  # asked for, but the scratch cannot hold the records
+        gqa.decode_plan(workspace_bytes=200 * rec, split_keys=gqa.SPLIT_EVEN, **kw)
+    assert e.value.status == -6
+    with pytest.raises(gqa.GqaError) as e:
+        gqa.decode_plan(**dict(kw, dtype=1, split_keys=gqa.SPLIT_EVEN))
+    assert e.value.status == -8
+    with pytest.raises(gqa.GqaError) as e:
+        gqa.decode_plan(**dict(kw, split_keys=-2))
+    assert e.value.status == -5
+    assert gqa.decode_plan(**dict(kw, seq_lens=None, plan_len_hint=8192))["even_cut"] == 0
 
 
 def test_planner_respects_overrides_and_workspace(gqa):
