@@ -793,7 +793,7 @@ def sweep_row(gqa, torch, name, timer, args, dev) -> dict:
                gbs=gbs, frac_of_measured_peak=gbs / peak, frac_of_8tbs_nominal=gbs / 8000.0,
                algorithmic_bytes=w.bytes_per_step(), split_chunks=w.plan["split_chunks"],
                ctas=w.plan["num_ctas"], cluster_size=w.plan.get("cluster_size", 0) if w.cluster_merge() else 0,
-               layers_cycled=w.slots,
+               even_cut=w.plan.get("even_cut", 0), layers_cycled=w.slots,
                launches_per_step=w.launches_per_step("peer"))
     if w.has_front:
         w.attention(0)
