@@ -74,7 +74,7 @@ def main() -> None:
     k_pool = H.rand_bits(rng, (num_blocks, hkv, block_tokens, d))
     v_pool = H.rand_bits(rng, (num_blocks, hkv, block_tokens, d))
 
-    def run(q_bits, k_bits, v_bits, heads_q, heads_kv, sharded):
+    def run(q_bits, k_bits, v_bits, heads_q, heads_kv, sharded, split_keys=512):
         layout = gqa.layout_pool(num_blocks, block_tokens, heads_kv)
         dq = H.bf16_tensor(q_bits, dev)
         dk, dv = H.bf16_tensor(k_bits, dev), H.bf16_tensor(v_bits, dev)
@@ -82,7 +82,7 @@ def main() -> None:
         ws = gqa.binding.workspace_for(batch, heads_q, heads_kv, dev)
         kw = dict(num_kv_heads=heads_kv, layout=layout, seq_lens=lens,
                   seq_lens_dev=torch.tensor(lens, dtype=torch.int32, device=dev),
-                  block_table=torch.from_numpy(table).to(dev), workspace=ws, split_keys=512)
+                  block_table=torch.from_numpy(table).to(dev), workspace=ws, split_keys=split_keys)
         if not sharded:
             gqa.decode(dq, dk, dv, out, **kw)
             torch.cuda.synchronize()
@@ -113,6 +113,11 @@ def main() -> None:
     for _ in range(5):
         again = run(q_l, k_l, v_l, per_q, per_kv, sharded=True)
         assert torch.equal(again.view(torch.int16), full.view(torch.int16)), "peer gather != unsharded"
+    # The even cut of the rank's own units (its summation order differs from the unsharded
+    # one, so the comparison is with the oracle), gathered through the same windows.
+    even = run(q_l, k_l, v_l, per_q, per_kv, sharded=True, split_keys=gqa.SPLIT_EVEN)
+    abs_err, rel_err = H.errors(even.float().cpu().numpy(), want)
+    assert abs_err <= 2e-2 and rel_err <= 1e-2, ("even cut, sharded", abs_err, rel_err)
     # The front stage inside the sharded attention kernel (gqa_decode_sharded_fused) against
     # the front kernel followed by gqa_decode_sharded: same gathered bits, same cache rows.
     layout_f = gqa.layout_pool(num_blocks, block_tokens, per_kv)
