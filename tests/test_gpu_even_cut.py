@@ -186,3 +186,47 @@ def test_even_cut_with_fused_front_and_two_tokens(gqa):
         lens_t = [n - tokens + 1 + t for n in lens]
         check(gqa, out_a[:, t], np.ascontiguousarray(H.bits_of(q_a)[:, t]), k_a, v_a, lens_t, layout,
               table, hkv, block_tokens)
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_batches(gqa, seed):
+    """Random batch sizes, lengths (some below one stage, some zero-padded to the block table's
+    capacity), groups, grid limits and query-token counts, through the even cut."""
+    rng = np.random.default_rng(1000 + seed)
+    hkv, block_tokens = 8, 256
+    group = int(rng.choice([1, 2, 4, 8]))
+    hq = hkv * group
+    tokens = int(rng.choice([1, 1, 2])) if group <= 8 else 1
+    if group * tokens > 16:
+        tokens = 1
+    batch = int(rng.integers(1, 9))
+    bps = int(rng.choice([2, 4, 8]))
+    cap = bps * block_tokens
+    lens = [int(rng.choice([tokens, tokens + 1, 63, 64, 65, int(rng.integers(tokens, cap + 1)), cap]))
+            for _ in range(batch)]
+    max_ctas = int(rng.choice([0, 0, 1, 7, 40]))
+    num_blocks = batch * bps
+    layout = gqa.layout_pool(num_blocks, block_tokens, hkv)
+    table = rng.permutation(num_blocks).reshape(batch, bps).astype(np.int32)
+    k = H.bf16_tensor(H.rand_bits(rng, (num_blocks, hkv, block_tokens, H.D)))
+    v = H.bf16_tensor(H.rand_bits(rng, (num_blocks, hkv, block_tokens, H.D)))
+    shape_q = (batch, hq, H.D) if tokens == 1 else (batch, tokens, hq, H.D)
+    q_bits = H.rand_bits(rng, shape_q)
+    plan = gqa.decode_plan(dtype=2, batch=batch, num_q_heads=hq, num_kv_heads=hkv, layout=layout,
+                           seq_lens=lens, blocks_per_seq=bps, paged=True, device_lens=True,
+                           q_tokens=tokens, max_ctas=max_ctas, split_keys=gqa.SPLIT_EVEN)
+    assert plan["even_cut"] == 1
+    ws = torch.full((plan["workspace_bytes"] // 4,), float("nan"), dtype=torch.float32, device="cuda:0")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    out = torch.full(shape_q, float("nan"), dtype=torch.bfloat16, device="cuda:0")
+    gqa.decode(H.bf16_tensor(q_bits), k, v, out, num_kv_heads=hkv, layout=layout, seq_lens=lens,
+               seq_lens_dev=torch.tensor(lens, dtype=torch.int32, device="cuda:0"),
+               block_table=torch.from_numpy(table).to("cuda:0"), workspace=ws, status=status,
+               max_ctas=max_ctas, split_keys=gqa.SPLIT_EVEN)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, (lens, group, tokens, max_ctas)
+    for t in range(tokens):
+        lens_t = [n - tokens + 1 + t for n in lens]
+        q_t = q_bits if tokens == 1 else np.ascontiguousarray(q_bits[:, t])
+        out_t = out if tokens == 1 else out[:, t]
+        check(gqa, out_t, q_t, k, v, lens_t, layout, table, hkv, block_tokens)
