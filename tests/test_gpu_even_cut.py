@@ -230,3 +230,34 @@ def test_random_batches(gqa, seed):
         q_t = q_bits if tokens == 1 else np.ascontiguousarray(q_bits[:, t])
         out_t = out if tokens == 1 else out[:, t]
         check(gqa, out_t, q_t, k, v, lens_t, layout, table, hkv, block_tokens)
+
+
+def test_planner_picks_it_for_the_ragged_benchmark_batch(gqa):
+    """BASELINE config 4 at full size (32 q / 8 kv heads, 16 sequences of 256-8192 keys in
+    256-token pool blocks), split left to the planner: it chooses the even cut, and every
+    sequence agrees with the oracle."""
+    import random
+    rnd = random.Random(20260614 + 4)
+    lens = [rnd.randint(256, 8192) for _ in range(16)]
+    rng = np.random.default_rng(44)
+    batch, hq, hkv, block_tokens, bps = 16, 32, 8, 256, 32
+    num_blocks = batch * bps
+    layout = gqa.layout_pool(num_blocks, block_tokens, hkv)
+    table = rng.permutation(num_blocks).reshape(batch, bps).astype(np.int32)
+    k = H.bf16_tensor(H.rand_bits(rng, (num_blocks, hkv, block_tokens, H.D)))
+    v = H.bf16_tensor(H.rand_bits(rng, (num_blocks, hkv, block_tokens, H.D)))
+    q_bits = H.rand_bits(rng, (batch, hq, H.D))
+    ws = gqa.binding.workspace_for(batch, hq, hkv, "cuda:0")
+    plan = gqa.decode_plan(dtype=2, batch=batch, num_q_heads=hq, num_kv_heads=hkv, layout=layout,
+                           seq_lens=lens, blocks_per_seq=bps, paged=True, device_lens=True,
+                           workspace_bytes=ws.numel() * 4)
+    assert plan["even_cut"] == 1 and plan["num_ctas"] == 148
+    status = torch.zeros(1, dtype=torch.int32, device="cuda:0")
+    out = torch.full((batch, hq, H.D), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+    gqa.decode(H.bf16_tensor(q_bits), k, v, out, num_kv_heads=hkv, layout=layout, seq_lens=lens,
+               seq_lens_dev=torch.tensor(lens, dtype=torch.int32, device="cuda:0"),
+               block_table=torch.from_numpy(table).to("cuda:0"), workspace=ws, status=status,
+               early_prefetch=True)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    check(gqa, out, q_bits, k, v, lens, layout, table, hkv, block_tokens)
